@@ -1,0 +1,240 @@
+/*
+ * mme_b200.h -- C ABI of the B200 (sm_100a) backend for the Gaudi MME compute reference.
+ *
+ * The reference's CPUCalculator (mme/mme_reference/mme_reference.h:108-191) keeps its C++
+ * signature; its private implementation (CPUCalculatorImpl, mme/mme_reference/mme_reference_impl.cpp)
+ * is the piece this library replaces. Every entry point below names the reference member it
+ * stands in for. All structs are plain data, all pointers are raw, no C++ or torch type crosses
+ * this boundary.
+ *
+ * Conventions shared with the reference:
+ *   - tensors have up to 5 dims, sizes[0] is the fastest (sim_tensor_base.h:52-54), strides are
+ *     in elements and strides[0] == 1;
+ *   - dtype / op / rounding / inf-nan values are the numeric values of the reference enums
+ *     (mme/include/mme_common/mme_common_enum.h:32-102,191-197,321-342);
+ *   - conv activations are [C,W,H,(D),B], weights are [K,C,S,R,(Q)], outputs [K,Wo,Ho,(Do),B]
+ *     (mme/include/general_utils.h:19-41).
+ *
+ * There is no CPU fallback: a call that cannot run on the GPU returns MMEB200_ERR_UNSUPPORTED
+ * or MMEB200_ERR_NO_DEVICE and leaves the output untouched.
+ */
+#ifndef MME_B200_H
+#define MME_B200_H
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MMEB200_MAX_DIMS 5
+#define MMEB200_MAX_CONV_DIMS 4
+
+/* ---- status codes (the C++ shim turns any non-zero status into MME_ASSERT(0, last_error),
+ *      mme/include/mme_assert.h:27-60) ---- */
+enum {
+    MMEB200_OK = 0,
+    MMEB200_ERR_INVALID_ARG = -1,
+    MMEB200_ERR_UNSUPPORTED = -2,
+    MMEB200_ERR_CUDA = -3,
+    MMEB200_ERR_TIMEOUT = -4,
+    MMEB200_ERR_NO_DEVICE = -5,
+    MMEB200_ERR_DEVICE_WAIT = -6 /* a bounded in-kernel wait gave up; context stays usable */
+};
+
+/* ---- EMmeDataType values (mme_common_enum.h:32-62) accepted by this backend ---- */
+enum {
+    MMEB200_FP8_143 = 9,
+    MMEB200_FP8_152 = 10,
+    MMEB200_BF16 = 12,
+    MMEB200_FP32 = 13,
+    MMEB200_FP32_IEEE = 14,
+    MMEB200_TF32 = 15
+};
+
+/* ---- EMmeOpType values (mme_common_enum.h:83-102) ---- */
+enum {
+    MMEB200_OP_FWD = 0,
+    MMEB200_OP_DEDX = 1,
+    MMEB200_OP_DEDW = 2,
+    MMEB200_OP_DETERMINISTIC_DEDW = 3,
+    MMEB200_OP_TRANSPOSED_DEDX = 4,
+    MMEB200_OP_AB = 5,
+    MMEB200_OP_ABT = 6,
+    MMEB200_OP_ATB = 7,
+    MMEB200_OP_ATBT = 8,
+    MMEB200_OP_MEMCPY = 10,
+    MMEB200_OP_TRANS = 11
+};
+
+/* ---- RoundingMode values (mme_common_enum.h:67-81) ---- */
+enum {
+    MMEB200_RM_NEAREST_EVEN = 0,
+    MMEB200_RM_TO_ZERO = 1,
+    MMEB200_RM_UP = 2,
+    MMEB200_RM_DOWN = 3,
+    MMEB200_RM_STOCHASTIC = 4,
+    MMEB200_RM_HALF_AWAY = 6,
+    MMEB200_RM_STOCHASTIC_RNE_DENORM = 7
+};
+
+/* ---- InfNanMode values (mme_common_enum.h:191-197) ---- */
+enum { MMEB200_INFNAN_FULL = 0, MMEB200_INFNAN_NONE = 1, MMEB200_INFNAN_MINIMAL = 2 };
+
+/* ---- EMmeReductionOp values (mme_common_enum.h:321-332) ---- */
+enum {
+    MMEB200_RED_ADD = 0,
+    MMEB200_RED_SUB = 1,
+    MMEB200_RED_MIN = 2,
+    MMEB200_RED_MAX = 3,
+    MMEB200_RED_MAX_0 = 4,
+    MMEB200_RED_NONE = 5
+};
+
+/* ---- ChipType values (mme_common_enum.h:25-30). The chip selects the reference's
+ *      accumulation model; this backend accumulates in fp32 on the tensor cores for all three
+ *      and accepts the value only so that callers need not change. ---- */
+enum { MMEB200_CHIP_GAUDI = 0, MMEB200_CHIP_GAUDI2 = 1, MMEB200_CHIP_GAUDI3 = 2 };
+
+/* where a tensor's bytes live */
+enum { MMEB200_MEM_HOST = 0, MMEB200_MEM_DEVICE = 1 };
+
+/* source of the random word used by the stochastic rounding modes */
+enum {
+    MMEB200_RNG_LFSR = 0,   /* the reference's per-lane Galois LFSRs: bit-exact, standalone cast only */
+    MMEB200_RNG_PHILOX = 1  /* counter-based Philox4x32-10 keyed by (seed, element index) */
+};
+
+/* Tensor descriptor: the plain-data image of MmeSimTensor (sim_tensor.h:9-52,
+ * sim_tensor_base.h:48-158). */
+typedef struct mmeb200_tensor {
+    int32_t dtype;                      /* EMmeDataType value */
+    int32_t dims;                       /* 1..5 */
+    uint32_t sizes[MMEB200_MAX_DIMS];   /* sizes[0] fastest; unused dims = 1 */
+    uint32_t strides[MMEB200_MAX_DIMS]; /* in elements; strides[0] == 1 */
+    uint32_t fp_bias;                   /* fp8 exponent bias (143: 3,7,11,15; 152: 1..30) */
+    int32_t inf_nan_mode;               /* InfNanMode value */
+    int32_t mem_space;                  /* MMEB200_MEM_HOST or MMEB200_MEM_DEVICE */
+    int32_t reserved;
+    void* data;
+} mmeb200_tensor;
+
+/* ConvolutionParams (convolution_params.h:7-29). Index 0 is the W axis, 1 = H, 2 = D. */
+typedef struct mmeb200_conv_params {
+    int32_t dim;
+    int32_t padding[MMEB200_MAX_CONV_DIMS];
+    int32_t stride[MMEB200_MAX_CONV_DIMS];
+    int32_t dilation[MMEB200_MAX_CONV_DIMS];
+    uint32_t padding_value; /* ignored for float dtypes: the reference forces 0 (mme_reference_impl.cpp:810-824) */
+    int32_t relu;
+} mmeb200_conv_params;
+
+/* The arguments of doActivation (mme_reference.h:162-172) that steer the fp32 -> out dtype cast. */
+typedef struct mmeb200_cast_params {
+    int32_t rounding;           /* RoundingMode value */
+    int32_t relu;
+    int32_t clip_fp;
+    int32_t clip_inf_in;
+    int32_t flush_denorms;
+    int32_t stochastic_ftz_fp8;
+    int32_t rng_kind;           /* MMEB200_RNG_* (used only by the stochastic modes) */
+    int32_t reserved;
+    uint64_t rng_seed;          /* Philox key */
+    uint64_t rng_offset;        /* Philox counter base: element i uses counter rng_offset + i */
+} mmeb200_cast_params;
+
+typedef struct mmeb200_ctx mmeb200_ctx;
+
+/* Replaces CPUCalculator::CPUCalculator (mme_reference_impl.cpp:129-200). `device` is a CUDA
+ * ordinal. seed / lfsr / polynomial have the reference's meaning: lfsr == NULL gives registers
+ * i+2, polynomial == 0 draws one in [25,63] from mt19937(seed). */
+int mmeb200_create(mmeb200_ctx** out_ctx, int chip, int device, unsigned seed,
+                   uint32_t lfsr_num_regs, const uint32_t* lfsr, uint32_t polynomial);
+void mmeb200_destroy(mmeb200_ctx* ctx);
+
+/* Run all later work of this context on the caller's CUDA stream (a cudaStream_t passed as
+ * void*); NULL goes back to the context's own stream. */
+int mmeb200_set_stream(mmeb200_ctx* ctx, void* cuda_stream);
+
+/* Replaces CPUCalculator::limitNumOfThreads (mme_reference_impl.cpp:2002-2012): kept for
+ * signature compatibility, a no-op on the GPU. */
+int mmeb200_limit_num_of_threads(mmeb200_ctx* ctx, unsigned n);
+
+/* Replaces CPUCalculator::doBatchGemm (mme_reference_impl.cpp:445-539), and with 2-dim tensors
+ * CPUCalculator::doGemm (:541-565). out->dtype == fp32 gives the reference's fp32 accumulator.
+ * When `cast` is non-NULL the epilogue also does what doActivation would do next
+ * (:661-689,1143-1245) and writes out->dtype directly (bf16 / fp8 / fp32). */
+int mmeb200_bgemm(mmeb200_ctx* ctx, mmeb200_tensor* out, const mmeb200_tensor* x,
+                  const mmeb200_tensor* w, int op, const mmeb200_cast_params* cast);
+
+/* Replaces CPUCalculator::doConvolution (mme_reference_impl.cpp:598-659): op is FWD, DEDX,
+ * DEDW or TRANSPOSED_DEDX; `out` is y, x or w respectively. `rounding` reaches only the fp32
+ * adds that merge filter taps in dedx (im2col.cpp:93-132). `cast` as in mmeb200_bgemm. */
+int mmeb200_conv(mmeb200_ctx* ctx, mmeb200_tensor* out, const mmeb200_tensor* x,
+                 const mmeb200_tensor* w, const mmeb200_tensor* y,
+                 const mmeb200_conv_params* params, int op, int rounding,
+                 const mmeb200_cast_params* cast);
+
+/* Replaces CPUCalculator::doActivation without ActivationParams (mme_reference_impl.cpp:661-689)
+ * -> convertToOutputDataType (:1143-1245): optional ReLU on the fp32 accumulator (in place, as
+ * the reference does), then the rounded cast. With rng_kind == MMEB200_RNG_LFSR the context's
+ * LFSR registers are used and advanced exactly like m_lfsr in the reference. */
+int mmeb200_activation(mmeb200_ctx* ctx, mmeb200_tensor* out, mmeb200_tensor* acc,
+                       const mmeb200_cast_params* cast);
+
+/* Replaces CPUCalculator::doMemoryWrite (mme_reference_impl.cpp:718-768): copy, or a
+ * read-modify-write reduction of mme_out into mem (fp32 and bf16). */
+int mmeb200_memory_write(mmeb200_ctx* ctx, mmeb200_tensor* mem, const mmeb200_tensor* mme_out,
+                         int reduction_op, int reduction_rm, int clip_fp);
+
+/* Bulk conversion utilities (the typed wrappers bf16_t / fp8_14x_t / fp32_t / tf32_t in
+ * mme/mme_reference/data_types, over coral-sim/src/gaudi3/fs_core/fs_fma.cpp:851-924,
+ * 6066-6140,6731-7029): fp8/bf16/tf32 -> fp32 decode, or fp32 -> any out dtype with `cast`. */
+int mmeb200_convert(mmeb200_ctx* ctx, mmeb200_tensor* out, const mmeb200_tensor* in,
+                    const mmeb200_cast_params* cast);
+
+/* Replaces CPUCalculator::doDma (mme_reference_impl.cpp:396-443): MEMCPY or TRANS (swap of the
+ * two fastest dims). */
+int mmeb200_dma(mmeb200_ctx* ctx, mmeb200_tensor* out, const mmeb200_tensor* x, int op);
+
+/* Read / overwrite the LFSR registers and polynomial (m_lfsr, m_polynomial,
+ * mme_reference_impl.h:251-253). */
+int mmeb200_get_lfsr(mmeb200_ctx* ctx, uint32_t* regs, uint32_t num_regs, uint32_t* polynomial);
+int mmeb200_set_lfsr(mmeb200_ctx* ctx, const uint32_t* regs, uint32_t num_regs, uint32_t polynomial);
+
+/* Wait, with a deadline, for everything queued on the context's stream; also collects the
+ * status word of the bounded in-kernel waits. No counterpart in the reference (it is
+ * synchronous); host-tensor calls sync internally. */
+int mmeb200_sync(mmeb200_ctx* ctx, uint64_t timeout_ns);
+
+/* Text of the last failure on this context (the message the shim hands to MME_ASSERT). */
+const char* mmeb200_last_error(const mmeb200_ctx* ctx);
+
+/* Device-memory helpers for callers that do not link the CUDA runtime (the benchmark and the
+ * multi-GPU driver keep operands resident with these). No counterpart in the reference. */
+int mmeb200_device_count(void);
+int mmeb200_malloc(mmeb200_ctx* ctx, void** dev_ptr, size_t bytes);
+int mmeb200_free(mmeb200_ctx* ctx, void* dev_ptr);
+int mmeb200_memcpy_h2d(mmeb200_ctx* ctx, void* dev_dst, const void* host_src, size_t bytes);
+int mmeb200_memcpy_d2h(mmeb200_ctx* ctx, void* host_dst, const void* dev_src, size_t bytes);
+int mmeb200_memset(mmeb200_ctx* ctx, void* dev_dst, int value, size_t bytes);
+/* Pinned host staging memory, so host-tensor calls copy at full PCIe rate. */
+int mmeb200_host_alloc(void** host_ptr, size_t bytes);
+int mmeb200_host_free(void* host_ptr);
+
+/* CUDA-event timing on the context's stream, for the benchmark: elapsed milliseconds between
+ * two recorded marks. */
+int mmeb200_timer_start(mmeb200_ctx* ctx);
+int mmeb200_timer_stop(mmeb200_ctx* ctx, float* elapsed_ms);
+
+/* Number of kernels this library has launched on the context since creation. */
+uint64_t mmeb200_launch_count(const mmeb200_ctx* ctx);
+
+/* Library version string, e.g. "mme_b200 0.1 sm_100a". */
+const char* mmeb200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MME_B200_H */
