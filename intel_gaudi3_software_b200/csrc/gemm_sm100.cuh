@@ -1,0 +1,399 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a. One kernel serves (batched) GEMM in all
+// four operand orientations and, through im2col-mode TMA loads, the implicit-GEMM convolutions
+// (forward, dedx and dedw). It stands in for the reference's per-element dot-product loop
+// (doMatrixMultiplicationFloat / doGemmWorkerFloat, mme/mme_reference/mme_reference_impl.cpp:914-956,
+// 1022-1053) and, with the fused epilogue, for the cast that doActivation performs afterwards
+// (mme_reference_impl.cpp:661-689,1143-1245).
+//
+// CTA layout (256 threads):
+//   warp 0      TMA producer: fills a ring of STAGES operand tiles (A: 128 x 128 B, B: BLOCK_N x 128 B,
+//               both 128-byte swizzled) and signals full[stage] through complete_tx.
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BLOCK_N, K=32 B) into one of
+//               two fp32 accumulators in tensor memory; tcgen05.commit frees the stage / publishes
+//               the accumulator.
+//   warp 2      allocates and frees tensor memory.
+//   warps 4-7   epilogue: tcgen05.ld the accumulator (lane = row), scale, optional ReLU + rounded
+//               cast, store. Runs concurrently with the next tile's main loop.
+// Tiles are walked in a grouped raster so that concurrently resident CTAs share operand panels
+// in L2. Every mbarrier wait is bounded; a wait that gives up writes a code to p.status and the
+// CTA leaves through the normal teardown.
+#pragma once
+#include "numerics.cuh"
+#include "ptx_sm100.cuh"
+
+namespace mmeb200 {
+
+constexpr int kBlockM = 128;
+constexpr int kRowBytes = 128;     // bytes of K per stage row = one swizzle span
+constexpr int kUmmaKBytes = 32;    // bytes of K consumed by one tcgen05.mma
+constexpr int kGemmThreads = 256;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+
+enum : uint32_t { A_TILED = 0, A_IM2COL = 1 };
+enum : uint32_t { KIND_F16 = 0, KIND_TF32 = 1, KIND_F8 = 2 };
+enum : uint32_t {
+    WAIT_OK = 0,
+    WAIT_PRODUCER_EMPTY = 1,
+    WAIT_MMA_FULL = 2,
+    WAIT_MMA_TMEM_EMPTY = 3,
+    WAIT_EPILOGUE_TMEM_FULL = 4
+};
+
+struct ConvGeom {
+    // A operand = activation tensor (C, W, H, N) read in im2col mode.
+    int32_t out_w, out_h;        // number of base positions per row / column (the GEMM's pixel grid)
+    int32_t stride_w, stride_h;  // traversal stride
+    int32_t lower_w, lower_h;    // coordinate of base position 0
+    int32_t dil_w, dil_h;
+    int32_t taps_w, taps_h;      // filter extent S, R
+    int32_t flip;                // 1: tap (s,r) uses offset (S-1-s, R-1-r) (dedx)
+    int32_t channels;            // C of the activation tensor
+    int32_t k_blocks_per_tap;    // fwd/dedx: k blocks that share a tap
+    int32_t b_tap_local;         // dedx: B's K coordinate restarts per tap, B rows advance by b_tap_rows
+    int32_t b_tap_rows;
+    int32_t pixels_along_k;      // dedw: pixels run along K, (tap, channel) along M
+};
+
+struct GemmParams {
+    CUtensorMap tm_a;
+    CUtensorMap tm_b;
+    uint32_t M, N, K;
+    uint32_t block_k;       // elements per k block (128 B / element size)
+    uint32_t num_k_blocks;  // over the whole K
+    uint32_t m_tiles, n_tiles, batches, split_k;
+    uint32_t bsz[3];
+    uint32_t a_bcast[3], b_bcast[3];
+    uint32_t a_mn_major, b_mn_major;
+    uint32_t a_mode;
+    uint32_t idesc;
+    uint32_t elem_bytes;
+    ConvGeom conv;
+    // epilogue
+    void* out;               // split_k == 1: final output; else fp32 workspace [split][batch][M][N]
+    uint32_t out_dtype;
+    uint32_t has_cast;
+    uint64_t out_ld;         // elements between output rows
+    uint64_t out_bstride[3]; // elements between batches
+    float scale;
+    CastSpec cast;
+    uint32_t rng_philox;
+    uint64_t rng_seed, rng_offset;
+    uint32_t* status;
+};
+
+template <int BLOCK_N, int STAGES>
+struct GemmSmem {
+    static constexpr int kABytes = kBlockM * kRowBytes;
+    static constexpr int kBBytes = BLOCK_N * kRowBytes;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kBarrierBytes = 256;
+    static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + 1024 /* alignment slack */;
+};
+
+struct TileCoord {
+    uint32_t m0, n0, batch, kb_begin, kb_end, split;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, uint32_t t) {
+    TileCoord c;
+    c.split = t % p.split_k;
+    t /= p.split_k;
+    const uint32_t per_batch = p.m_tiles * p.n_tiles;
+    c.batch = t / per_batch;
+    const uint32_t r = t % per_batch;
+    constexpr uint32_t GM = 16;
+    const uint32_t group_span = GM * p.n_tiles;
+    const uint32_t first_m = (r / group_span) * GM;
+    const uint32_t gsz = min(GM, p.m_tiles - first_m);
+    const uint32_t in_group = r % group_span;
+    c.m0 = (first_m + in_group % gsz) * kBlockM;
+    c.n0 = (in_group / gsz);  // tile index; scaled by the caller's BLOCK_N
+    const uint32_t per_split = (p.num_k_blocks + p.split_k - 1) / p.split_k;
+    c.kb_begin = c.split * per_split;
+    c.kb_end = min(p.num_k_blocks, c.kb_begin + per_split);
+    return c;
+}
+
+template <int KIND, int BLOCK_N, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
+    using S = GemmSmem<BLOCK_N, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * S::kStageBytes);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* tmem_full_bar = empty_bar + STAGES;
+    uint64_t* tmem_empty_bar = tmem_full_bar + 2;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t total_tiles = p.m_tiles * p.n_tiles * p.batches * p.split_k;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tmem_full_bar[b], 1);
+            mbar_init(&tmem_empty_bar[b], 128);
+        }
+        fence_mbar_init();
+        tma_prefetch_desc(&p.tm_a);
+        tma_prefetch_desc(&p.tm_b);
+    }
+    if (warp == 2) {
+        tmem_alloc(tmem_holder, 2 * BLOCK_N);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            const uint32_t a_groups = p.a_mn_major ? (kBlockM * p.elem_bytes) / kRowBytes : 1;
+            const uint32_t b_groups = p.b_mn_major ? (BLOCK_N * p.elem_bytes) / kRowBytes : 1;
+            const uint32_t mn_group_elems = kRowBytes / p.elem_bytes;
+            const uint32_t mn_group_bytes = p.block_k * kRowBytes;
+            for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const TileCoord tc = decode_tile(p, t);
+                const uint32_t n0 = tc.n0 * BLOCK_N;
+                uint32_t bi[3];
+                {
+                    uint32_t b = tc.batch;
+                    bi[0] = b % p.bsz[0]; b /= p.bsz[0];
+                    bi[1] = b % p.bsz[1]; b /= p.bsz[1];
+                    bi[2] = b;
+                }
+                // im2col: base position of the tile's first pixel (fwd / dedx)
+                int pw = 0, ph = 0, pn = 0;
+                if (p.a_mode == A_IM2COL && !p.conv.pixels_along_k) {
+                    const uint32_t q = tc.m0 % p.conv.out_w;
+                    const uint32_t rest = tc.m0 / p.conv.out_w;
+                    pw = int(q) * p.conv.stride_w + p.conv.lower_w;
+                    ph = int(rest % p.conv.out_h) * p.conv.stride_h + p.conv.lower_h;
+                    pn = int(rest / p.conv.out_h);
+                }
+                for (uint32_t kb = tc.kb_begin; kb < tc.kb_end; ++kb) {
+                    if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, kWaitLimitNs)) {
+                        atomicCAS(p.status, 0u, WAIT_PRODUCER_EMPTY);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* a_dst = smem + stage * S::kStageBytes;
+                    uint8_t* b_dst = a_dst + S::kABytes;
+                    mbar_arrive_expect_tx(&full_bar[stage], S::kStageBytes);
+                    uint32_t k_elem = kb * p.block_k;  // K coordinate for plain operands
+                    uint32_t tap = 0, k_in_tap = k_elem;
+                    if (p.a_mode == A_IM2COL && !p.conv.pixels_along_k) {
+                        tap = kb / p.conv.k_blocks_per_tap;
+                        k_in_tap = (kb % p.conv.k_blocks_per_tap) * p.block_k;
+                    }
+                    // ---- A
+                    if (p.a_mode == A_TILED) {
+                        const int b0 = p.a_bcast[0] ? 0 : bi[0], b1 = p.a_bcast[1] ? 0 : bi[1], b2 = p.a_bcast[2] ? 0 : bi[2];
+                        if (!p.a_mn_major) {
+                            tma_load_5d(a_dst, &p.tm_a, &full_bar[stage], k_elem, tc.m0, b0, b1, b2);
+                        } else {
+                            for (uint32_t g = 0; g < a_groups; ++g)
+                                tma_load_5d(a_dst + g * mn_group_bytes, &p.tm_a, &full_bar[stage],
+                                            tc.m0 + g * mn_group_elems, k_elem, b0, b1, b2);
+                        }
+                    } else if (!p.conv.pixels_along_k) {
+                        int s = int(tap % p.conv.taps_w), r = int(tap / p.conv.taps_w);
+                        if (p.conv.flip) { s = p.conv.taps_w - 1 - s; r = p.conv.taps_h - 1 - r; }
+                        tma_load_im2col_4d(a_dst, &p.tm_a, &full_bar[stage], int(k_in_tap), pw, ph, pn,
+                                           uint16_t(s * p.conv.dil_w), uint16_t(r * p.conv.dil_h));
+                    } else {
+                        // dedw: rows of the tile are (tap, channel); k runs over pixels
+                        const uint32_t pix = k_elem;
+                        const uint32_t q = pix % p.conv.out_w;
+                        const uint32_t rest = pix / p.conv.out_w;
+                        const int w0 = int(q) * p.conv.stride_w + p.conv.lower_w;
+                        const int h0 = int(rest % p.conv.out_h) * p.conv.stride_h + p.conv.lower_h;
+                        const int n0i = int(rest / p.conv.out_h);
+                        for (uint32_t g = 0; g < a_groups; ++g) {
+                            const uint32_t m = tc.m0 + g * mn_group_elems;
+                            const uint32_t tp = m / p.conv.channels, c = m % p.conv.channels;
+                            const int s = int(tp % p.conv.taps_w), r = int(tp / p.conv.taps_w);
+                            tma_load_im2col_4d(a_dst + g * mn_group_bytes, &p.tm_a, &full_bar[stage], int(c), w0, h0, n0i,
+                                               uint16_t(s * p.conv.dil_w), uint16_t(r * p.conv.dil_h));
+                        }
+                    }
+                    // ---- B
+                    {
+                        const int b0 = p.b_bcast[0] ? 0 : bi[0], b1 = p.b_bcast[1] ? 0 : bi[1], b2 = p.b_bcast[2] ? 0 : bi[2];
+                        if (!p.b_mn_major) {
+                            const uint32_t kc = p.conv.b_tap_local ? k_in_tap : k_elem;
+                            const uint32_t row = n0 + (p.conv.b_tap_local ? tap * p.conv.b_tap_rows : 0);
+                            tma_load_5d(b_dst, &p.tm_b, &full_bar[stage], kc, row, b0, b1, b2);
+                        } else {
+                            for (uint32_t g = 0; g < b_groups; ++g)
+                                tma_load_5d(b_dst + g * mn_group_bytes, &p.tm_b, &full_bar[stage], n0 + g * mn_group_elems,
+                                            k_elem, b0, b1, b2);
+                        }
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            const uint32_t mn_k_step = (kUmmaKBytes / p.elem_bytes) * kRowBytes;  // MN-major: bytes per MMA along K
+            const uint32_t mn_lbo = p.block_k * kRowBytes;
+            for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const TileCoord tc = decode_tile(p, t);
+                if (!mbar_wait_bounded(&tmem_empty_bar[acc], acc_phase ^ 1, kWaitLimitNs)) {
+                    atomicCAS(p.status, 0u, WAIT_MMA_TMEM_EMPTY);
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
+                for (uint32_t kb = tc.kb_begin; kb < tc.kb_end; ++kb) {
+                    if (!mbar_wait_bounded(&full_bar[stage], phase, kWaitLimitNs)) {
+                        atomicCAS(p.status, 0u, WAIT_MMA_FULL);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_base = smem_u32(smem + stage * S::kStageBytes);
+                    const uint32_t b_base = a_base + S::kABytes;
+#pragma unroll
+                    for (uint32_t k = 0; k < kRowBytes / kUmmaKBytes; ++k) {
+                        const uint64_t a_desc = p.a_mn_major ? make_smem_desc(a_base + k * mn_k_step, mn_lbo, 1024)
+                                                             : make_smem_desc(a_base + k * kUmmaKBytes, 16, 1024);
+                        const uint64_t b_desc = p.b_mn_major ? make_smem_desc(b_base + k * mn_k_step, mn_lbo, 1024)
+                                                             : make_smem_desc(b_base + k * kUmmaKBytes, 16, 1024);
+                        umma_ss<KIND>(d_tmem, a_desc, b_desc, p.idesc, (kb > tc.kb_begin || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[stage]);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit(&tmem_full_bar[acc]);
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1;
+            }
+        }
+        __syncwarp();
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------------ epilogue
+        const uint32_t sub = warp & 3;  // tensor-memory sub-partition this warp may read
+        uint32_t acc = 0, acc_phase = 0;
+        const uint32_t out_elem = dtype_size(int(p.out_dtype));
+        for (uint32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+            const TileCoord tc = decode_tile(p, t);
+            const uint32_t n0 = tc.n0 * BLOCK_N;
+            if (!mbar_wait_bounded(&tmem_full_bar[acc], acc_phase, kWaitLimitNs)) {
+                atomicCAS(p.status, 0u, WAIT_EPILOGUE_TMEM_FULL);
+                break;
+            }
+            tc_fence_after_sync();
+            const uint32_t row = tc.m0 + sub * 32 + lane;
+            uint64_t base_off;
+            if (p.split_k > 1) {
+                base_off = (uint64_t(tc.split) * p.batches + tc.batch) * uint64_t(p.M) * p.N + uint64_t(row) * p.N;
+            } else {
+                uint32_t b = tc.batch;
+                const uint32_t i0 = b % p.bsz[0]; b /= p.bsz[0];
+                const uint32_t i1 = b % p.bsz[1]; b /= p.bsz[1];
+                base_off = i0 * p.out_bstride[0] + i1 * p.out_bstride[1] + b * p.out_bstride[2] + uint64_t(row) * p.out_ld;
+            }
+            const uint64_t flat_row = (uint64_t(tc.batch) * p.M + row) * p.N;  // index base for the random stream
+#pragma unroll 1
+            for (uint32_t ch = 0; ch < BLOCK_N / 32; ++ch) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(tmem_base + acc * BLOCK_N + ch * 32 + ((sub * 32) << 16), v);
+                tmem_ld_wait();
+                const uint32_t col0 = n0 + ch * 32;
+                if (row < p.M && col0 < p.N) {
+                    const uint32_t ncols = min(32u, p.N - col0);
+                    if (p.split_k > 1) {
+                        float* dst = reinterpret_cast<float*>(p.out) + base_off + col0;
+                        if (ncols == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        } else {
+                            for (uint32_t j = 0; j < ncols; ++j) dst[j] = __uint_as_float(v[j]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            uint32_t bits = __float_as_uint(__uint_as_float(v[j]) * p.scale);
+                            if (f32_is_nan(bits)) bits = kF32CanonNan;
+                            if (p.has_cast) {
+                                if (p.cast.relu) bits = relu_bits(bits);
+                                uint32_t rnd = 0;
+                                if (p.rng_philox) rnd = philox_word(p.rng_seed, p.rng_offset, flat_row + col0 + j);
+                                bits = cast_from_f32(bits, p.cast, rnd);
+                            }
+                            v[j] = bits;
+                        }
+                        uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) + (base_off + col0) * out_elem;
+                        const bool vec_ok = ncols == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+                        if (out_elem == 4) {
+                            if (vec_ok) {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j)
+                                    reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                            } else {
+                                for (uint32_t j = 0; j < ncols; ++j) reinterpret_cast<uint32_t*>(dst)[j] = v[j];
+                            }
+                        } else if (out_elem == 2) {
+                            if (vec_ok) {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    uint4 w;
+                                    w.x = (v[8 * j + 0] & 0xFFFF) | (v[8 * j + 1] << 16);
+                                    w.y = (v[8 * j + 2] & 0xFFFF) | (v[8 * j + 3] << 16);
+                                    w.z = (v[8 * j + 4] & 0xFFFF) | (v[8 * j + 5] << 16);
+                                    w.w = (v[8 * j + 6] & 0xFFFF) | (v[8 * j + 7] << 16);
+                                    reinterpret_cast<uint4*>(dst)[j] = w;
+                                }
+                            } else {
+                                for (uint32_t j = 0; j < ncols; ++j) reinterpret_cast<uint16_t*>(dst)[j] = uint16_t(v[j]);
+                            }
+                        } else {
+                            if (vec_ok) {
+#pragma unroll
+                                for (int j = 0; j < 2; ++j) {
+                                    uint4 w;
+                                    w.x = (v[16 * j + 0] & 0xFF) | ((v[16 * j + 1] & 0xFF) << 8) | ((v[16 * j + 2] & 0xFF) << 16) | (v[16 * j + 3] << 24);
+                                    w.y = (v[16 * j + 4] & 0xFF) | ((v[16 * j + 5] & 0xFF) << 8) | ((v[16 * j + 6] & 0xFF) << 16) | (v[16 * j + 7] << 24);
+                                    w.z = (v[16 * j + 8] & 0xFF) | ((v[16 * j + 9] & 0xFF) << 8) | ((v[16 * j + 10] & 0xFF) << 16) | (v[16 * j + 11] << 24);
+                                    w.w = (v[16 * j + 12] & 0xFF) | ((v[16 * j + 13] & 0xFF) << 8) | ((v[16 * j + 14] & 0xFF) << 16) | (v[16 * j + 15] << 24);
+                                    reinterpret_cast<uint4*>(dst)[j] = w;
+                                }
+                            } else {
+                                for (uint32_t j = 0; j < ncols; ++j) dst[j] = uint8_t(v[j]);
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&tmem_empty_bar[acc]);
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1;
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 2 * BLOCK_N);
+    }
+}
+
+}  // namespace mmeb200

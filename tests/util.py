@@ -1,0 +1,94 @@
+"""Shared helpers of the test-suite: seeded inputs in the reference's formats, decoders, and the
+comparison rules of the parity tests.
+
+Tolerances (stated here once, used by every accumulation test):
+  * fp32 accumulators: |gpu - ref| <= ACC_TOL * sum_k |a_k * b_k| per element (1e-5, the north
+    star's "<= 1e-5 relative error on fp32 accumulators", taken norm-wise because the reference's
+    own truncating accumulation sits up to ~1e-6 * sum|ab| away from the exact dot product);
+  * rounded outputs: bit-exact, or at most 1 ulp of the output type, or (near cancellation, where
+    an accumulator difference of 1e-5 * sum|ab| spans many ulps of a tiny result) within the
+    accumulator tolerance.
+"""
+import numpy as np
+
+from intel_gaudi3_software_b200 import abi
+
+ACC_TOL = 1e-5
+
+
+def bf16_to_f32(u16):
+    return (np.asarray(u16, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16_rne(x):
+    """Round-to-nearest-even fp32 -> bf16 bit patterns (finite inputs; same result as fp32_to_bf16 RNE)."""
+    b = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    r = ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
+    return r
+
+
+def decode(arr, dtype, bias=0, mode=0, oracle=None):
+    if dtype == abi.BF16:
+        return bf16_to_f32(arr)
+    if dtype in (abi.FP8_143, abi.FP8_152):
+        assert oracle is not None
+        return oracle.fp8_to_fp32(np.asarray(arr, dtype=np.uint8), 4 if dtype == abi.FP8_143 else 5, bias, mode)
+    return np.asarray(arr, dtype=np.float32)
+
+
+def gen_bf16(rng, n, dist="uniform", scale=1.0):
+    v = rng.uniform(-1, 1, n) if dist == "uniform" else rng.normal(0, scale, n)
+    return f32_to_bf16_rne(v.astype(np.float32))
+
+
+def gen_fp8(rng, n, oracle, dtype=abi.FP8_143, bias=7, mode=abi.INFNAN_MINIMAL, amax_target=None):
+    """N(0,1) scaled so that amax lands on the format's largest finite value, RNE-cast (BASELINE config 2)."""
+    v = rng.normal(0, 1, n).astype(np.float32)
+    ew = 4 if dtype == abi.FP8_143 else 5
+    if amax_target is None:
+        if dtype == abi.FP8_143:
+            amax_target = (448.0 if mode != 0 else 240.0) * 2.0 ** (7 - bias)
+        else:
+            amax_target = 57344.0 * 2.0 ** (15 - bias)
+    v *= np.float32(amax_target / np.abs(v).max())
+    return oracle.fp32_to_fp8(v, ew, bias, abi.RM_NE, None, False, True, False, False, mode)
+
+
+def sum_abs_products(a_f32, b_f32):
+    """sum_k |a_ik| |b_kj| in float64: the scale of the accumulation tolerance."""
+    return np.abs(a_f32.astype(np.float64)) @ np.abs(b_f32.astype(np.float64))
+
+
+def acc_error(gpu, ref, sabs):
+    """max over elements of |gpu-ref| / sum|ab| (elements with sum|ab| == 0 must match exactly)."""
+    g, r = gpu.astype(np.float64), ref.astype(np.float64)
+    both_nan = np.isnan(g) & np.isnan(r)
+    d = np.abs(g - r)
+    d[both_nan] = 0
+    d[(g == r)] = 0  # equal infinities
+    with np.errstate(divide="ignore", invalid="ignore"):
+        rel = np.where(sabs > 0, d / sabs, np.where(d == 0, 0.0, np.inf))
+    return float(np.nanmax(rel)) if rel.size else 0.0
+
+
+def ulp_diff_bits(a_bits, b_bits, width):
+    """Distance in representable values between two sign-magnitude bit patterns of `width` bits."""
+    a = np.asarray(a_bits).astype(np.int64)
+    b = np.asarray(b_bits).astype(np.int64)
+    sign = 1 << (width - 1)
+    ai = np.where(a & sign, -(a & (sign - 1)), a & (sign - 1))
+    bi = np.where(b & sign, -(b & (sign - 1)), b & (sign - 1))
+    return np.abs(ai - bi)
+
+
+def check_rounded(gpu_bits, ref_bits, width, gpu_val, ref_val, sabs, name=""):
+    """The rounded-output rule above. Returns (n_inexact, n_beyond_1ulp_but_within_acc_tol)."""
+    ud = ulp_diff_bits(gpu_bits, ref_bits, width)
+    inexact = int((ud != 0).sum())
+    far = ud > 1
+    if far.any():
+        d = np.abs(gpu_val.astype(np.float64) - ref_val.astype(np.float64))
+        bad = far & ~(d <= ACC_TOL * sabs)
+        assert not bad.any(), "%s: %d outputs differ by more than 1 ulp and more than the accumulator tolerance" % (
+            name, int(bad.sum()))
+    return inexact, int(far.sum())
