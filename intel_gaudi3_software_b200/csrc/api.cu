@@ -332,6 +332,10 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     p.out_dtype = o.dtype;
     p.has_cast = o.has_cast;
     p.cast = o.cast;
+    if (!o.has_cast) p.epi_mode = EPI_F32;
+    else if (o.cast.out_dtype == DT_BF16 && o.cast.rm == RM_NE && !o.cast.relu && !o.cast.clip && !o.cast.ftz) p.epi_mode = EPI_BF16_RNE;
+    else if (o.cast.out_dtype == DT_FP32 && !o.cast.relu && !o.cast.clip && !o.cast.ftz) p.epi_mode = EPI_F32;
+    else p.epi_mode = EPI_GENERIC;
     p.rng_philox = o.philox;
     p.rng_seed = o.seed;
     p.rng_offset = o.offset;
@@ -830,7 +834,6 @@ static int conv_fast_path(mmeb200_ctx* c, const mmeb200_tensor* x, const mmeb200
                           const mmeb200_conv_params* p, int op, GemmJob* job, float* scale, bool* taken) {
     *taken = false;
     const mmeb200_tensor* act = (op == MMEB200_OP_DEDX) ? y : x;   // tensor read through im2col TMA
-    const mmeb200_tensor* grid = (op == MMEB200_OP_DEDX) ? x : y;  // tensor whose (W,H,B) positions are the pixels
     const mmeb200_tensor* other = (op == MMEB200_OP_DEDW) ? y : w; // the plain (tiled) operand
     if (p->dim != 2 || x->dims != 4 || y->dims != 4 || w->dims != 4) return 0;
     if (!(act->dtype == DT_BF16 || dtype_is_fp8(act->dtype))) return 0;
@@ -941,7 +944,6 @@ static int conv_fast_path(mmeb200_ctx* c, const mmeb200_tensor* x, const mmeb200
                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return 0;  // geometry outside what the copy engine takes: general path
-    (void) grid;
     *taken = true;
     return 0;
 }

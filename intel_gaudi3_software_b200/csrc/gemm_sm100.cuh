@@ -31,6 +31,7 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 
 enum : uint32_t { A_TILED = 0, A_IM2COL = 1 };
 enum : uint32_t { KIND_F16 = 0, KIND_TF32 = 1, KIND_F8 = 2 };
+enum : uint32_t { EPI_GENERIC = 0, EPI_F32 = 1, EPI_BF16_RNE = 2 };
 enum : uint32_t {
     WAIT_OK = 0,
     WAIT_PRODUCER_EMPTY = 1,
@@ -72,6 +73,7 @@ struct GemmParams {
     void* out;               // split_k == 1: final output; else fp32 workspace [split][batch][M][N]
     uint32_t out_dtype;
     uint32_t has_cast;
+    uint32_t epi_mode;       // EPI_*: which epilogue body applies (uniform per launch)
     uint64_t out_ld;         // elements between output rows
     uint64_t out_bstride[3]; // elements between batches
     float scale;
@@ -315,68 +317,72 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
                 tmem_ld_32x32b_x32(tmem_base + acc * BLOCK_N + ch * 32 + ((sub * 32) << 16), v);
                 tmem_ld_wait();
                 const uint32_t col0 = n0 + ch * 32;
-                if (row < p.M && col0 < p.N) {
-                    const uint32_t ncols = min(32u, p.N - col0);
-                    if (p.split_k > 1) {
-                        float* dst = reinterpret_cast<float*>(p.out) + base_off + col0;
-                        if (ncols == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+                if (row >= p.M || col0 >= p.N) continue;
+                const uint32_t ncols = min(32u, p.N - col0);
+                uint32_t elem = 4;
+                uint8_t* dst;
+                if (p.split_k > 1) {
+                    dst = reinterpret_cast<uint8_t*>(reinterpret_cast<float*>(p.out) + base_off + col0);
+                } else {
+                    elem = out_elem;
+                    dst = reinterpret_cast<uint8_t*>(p.out) + (base_off + col0) * out_elem;
+                    if (p.epi_mode == EPI_BF16_RNE) {
+                        // round-to-nearest-even with no flags: the hardware conversion gives the
+                        // reference's bits (NaN -> 0x7FFF, denormals kept)
 #pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                        } else {
-                            for (uint32_t j = 0; j < ncols; ++j) dst[j] = __uint_as_float(v[j]);
+                        for (int j = 0; j < 16; ++j) {
+                            const float lo = __uint_as_float(v[2 * j]) * p.scale, hi = __uint_as_float(v[2 * j + 1]) * p.scale;
+                            uint32_t packed;
+                            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
+                            v[j] = packed;
+                        }
+                    } else if (p.epi_mode == EPI_F32) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            uint32_t bits = __float_as_uint(__uint_as_float(v[j]) * p.scale);
+                            v[j] = f32_is_nan(bits) ? kF32CanonNan : bits;
                         }
                     } else {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             uint32_t bits = __float_as_uint(__uint_as_float(v[j]) * p.scale);
                             if (f32_is_nan(bits)) bits = kF32CanonNan;
-                            if (p.has_cast) {
-                                if (p.cast.relu) bits = relu_bits(bits);
-                                uint32_t rnd = 0;
-                                if (p.rng_philox) rnd = philox_word(p.rng_seed, p.rng_offset, flat_row + col0 + j);
-                                bits = cast_from_f32(bits, p.cast, rnd);
-                            }
-                            v[j] = bits;
+                            if (p.cast.relu) bits = relu_bits(bits);
+                            uint32_t rnd = 0;
+                            if (p.rng_philox) rnd = philox_word(p.rng_seed, p.rng_offset, flat_row + col0 + j);
+                            v[j] = cast_from_f32(bits, p.cast, rnd);
                         }
-                        uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) + (base_off + col0) * out_elem;
-                        const bool vec_ok = ncols == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
-                        if (out_elem == 4) {
-                            if (vec_ok) {
+                        // pack to the output width
+                        if (elem == 2) {
 #pragma unroll
-                                for (int j = 0; j < 8; ++j)
-                                    reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                            } else {
-                                for (uint32_t j = 0; j < ncols; ++j) reinterpret_cast<uint32_t*>(dst)[j] = v[j];
-                            }
-                        } else if (out_elem == 2) {
-                            if (vec_ok) {
+                            for (int j = 0; j < 16; ++j) v[j] = (v[2 * j] & 0xFFFFu) | (v[2 * j + 1] << 16);
+                        } else if (elem == 1) {
 #pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    uint4 w;
-                                    w.x = (v[8 * j + 0] & 0xFFFF) | (v[8 * j + 1] << 16);
-                                    w.y = (v[8 * j + 2] & 0xFFFF) | (v[8 * j + 3] << 16);
-                                    w.z = (v[8 * j + 4] & 0xFFFF) | (v[8 * j + 5] << 16);
-                                    w.w = (v[8 * j + 6] & 0xFFFF) | (v[8 * j + 7] << 16);
-                                    reinterpret_cast<uint4*>(dst)[j] = w;
-                                }
-                            } else {
-                                for (uint32_t j = 0; j < ncols; ++j) reinterpret_cast<uint16_t*>(dst)[j] = uint16_t(v[j]);
-                            }
-                        } else {
-                            if (vec_ok) {
+                            for (int j = 0; j < 8; ++j)
+                                v[j] = (v[4 * j] & 0xFFu) | ((v[4 * j + 1] & 0xFFu) << 8) | ((v[4 * j + 2] & 0xFFu) << 16) | (v[4 * j + 3] << 24);
+                        }
+                    }
+                }
+                // v[0 .. 8*elem) now holds 32 packed outputs
+                if (ncols == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+                    if (elem == 4) {
 #pragma unroll
-                                for (int j = 0; j < 2; ++j) {
-                                    uint4 w;
-                                    w.x = (v[16 * j + 0] & 0xFF) | ((v[16 * j + 1] & 0xFF) << 8) | ((v[16 * j + 2] & 0xFF) << 16) | (v[16 * j + 3] << 24);
-                                    w.y = (v[16 * j + 4] & 0xFF) | ((v[16 * j + 5] & 0xFF) << 8) | ((v[16 * j + 6] & 0xFF) << 16) | (v[16 * j + 7] << 24);
-                                    w.z = (v[16 * j + 8] & 0xFF) | ((v[16 * j + 9] & 0xFF) << 8) | ((v[16 * j + 10] & 0xFF) << 16) | (v[16 * j + 11] << 24);
-                                    w.w = (v[16 * j + 12] & 0xFF) | ((v[16 * j + 13] & 0xFF) << 8) | ((v[16 * j + 14] & 0xFF) << 16) | (v[16 * j + 15] << 24);
-                                    reinterpret_cast<uint4*>(dst)[j] = w;
-                                }
-                            } else {
-                                for (uint32_t j = 0; j < ncols; ++j) dst[j] = uint8_t(v[j]);
-                            }
+                        for (int j = 0; j < 8; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    } else if (elem == 2) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    }
+                } else {
+                    // ragged edge or unaligned row: element-wise, statically indexed
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (uint32_t(j) < ncols) {
+                            if (elem == 4) reinterpret_cast<uint32_t*>(dst)[j] = v[j];
+                            else if (elem == 2) reinterpret_cast<uint16_t*>(dst)[j] = uint16_t(v[j / 2] >> (16 * (j & 1)));
+                            else dst[j] = uint8_t(v[j / 4] >> (8 * (j & 3)));
                         }
                     }
                 }

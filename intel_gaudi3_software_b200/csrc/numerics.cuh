@@ -60,7 +60,7 @@ MME_HD uint32_t fp8_decode(uint32_t v, int exp_width, int bias, int mode) {
 MME_HD bool fp8_code_is_foreign(uint32_t v, int exp_width, int mode) {
     const uint32_t a = v & 0x7Fu;
     if (exp_width == 4) {  // hardware: only 0x7f is NaN, no Inf
-        if (mode == 0) return a >= 0x78u;
+        if (mode == 0) return a >= 0x78u && a != 0x7Fu;
         if (mode == 1) return a == 0x7Fu;
         return false;
     }

@@ -1,0 +1,37 @@
+// TEST INFRASTRUCTURE: compiles the product's device conversion functions (csrc/numerics.cuh, which
+// are __host__ __device__) for the host, so that their bit patterns can be compared against the CPU
+// oracle on a machine without a GPU. Nothing in the product links or calls this file.
+#include <cstddef>
+#include <cstdint>
+
+#include "numerics.cuh"
+
+using namespace mmeb200;
+
+extern "C" {
+void hc_fp8_decode(const uint8_t* in, uint32_t* out, size_t n, int exp_width, int bias, int mode)
+{
+    for (size_t i = 0; i < n; i++) out[i] = fp8_decode(in[i], exp_width, bias, mode);
+}
+void hc_cast(const uint32_t* in, uint8_t* out, size_t n, int out_dtype, int exp_width, int bias, int mode, int rm, int relu, int clip,
+             int clip_inf_in, int ftz, int sftz, const uint32_t* rnd)
+{
+    CastSpec c{out_dtype, exp_width, bias, mode, rm, relu, clip, clip_inf_in, ftz, sftz};
+    const int es = dtype_size(out_dtype);
+    for (size_t i = 0; i < n; i++) {
+        uint32_t b = in[i];
+        if (relu) b = relu_bits(b);
+        const uint32_t v = cast_from_f32(b, c, rnd ? rnd[i] : 0);
+        for (int k = 0; k < es; k++) out[i * es + k] = uint8_t(v >> (8 * k));
+    }
+}
+int hc_fp8_foreign(uint32_t code, int exp_width, int mode) { return fp8_code_is_foreign(code, exp_width, mode); }
+uint32_t hc_lfsr(uint32_t v, uint32_t poly) { return lfsr32_step(v, poly); }
+uint32_t hc_philox(uint64_t seed, uint64_t offset, uint64_t index) { return philox_word(seed, offset, index); }
+void hc_philox_block(uint32_t* c, uint32_t k0, uint32_t k1)
+{
+    uint32_t s[4] = {c[0], c[1], c[2], c[3]};
+    philox4x32_10(s, k0, k1);
+    for (int i = 0; i < 4; i++) c[i] = s[i];
+}
+}

@@ -1,0 +1,217 @@
+"""The benchmark configurations at their full sizes on the GPU, checked (a) against the CPU oracle on
+slices that keep the common dimension whole, so every checked output sees the complete, identically
+ordered reduction, and (b) through size-independent properties at full size."""
+import numpy as np
+import pytest
+
+from intel_gaudi3_software_b200 import abi
+from intel_gaudi3_software_b200.abi import make_tensor as T
+import bench
+import util
+
+pytestmark = pytest.mark.gpu
+
+
+def rows_for(oracle, macs_per_row, budget_macs=1.2e9):
+    t = max(1, oracle.hardware_threads())
+    rows = int(max(8, min(256, budget_macs * min(t, 16) / 8 / macs_per_row)))
+    return rows
+
+
+def test_config1_bf16_gemm_1024_full(calc, best_oracle):
+    """Config 1 in full: bf16 1024^3, uniform[-1,1], fp32 output."""
+    rng = np.random.default_rng(1)
+    n = 1024
+    xb, wb = util.gen_bf16(rng, n * n), util.gen_bf16(rng, n * n)
+    x, w = T(xb, abi.BF16, [n, n]), T(wb, abi.BF16, [n, n])
+    o = np.zeros(n * n, np.float32)
+    calc.do_batch_gemm(T(o, abi.FP32, [n, n]), x, w, abi.OP_AB)
+    rows = rows_for(best_oracle, n * n, 4e8)
+    r = np.zeros(rows * n, np.float32)
+    assert best_oracle.bgemm(T(r, abi.FP32, [n, rows]), T(xb[:rows * n], abi.BF16, [n, rows]), w, abi.OP_AB) == 0
+    sabs = util.sum_abs_products(util.bf16_to_f32(xb).reshape(n, n)[:rows], util.bf16_to_f32(wb).reshape(n, n))
+    assert util.acc_error(o.reshape(n, n)[:rows], r.reshape(rows, n), sabs) <= util.ACC_TOL
+    # full-size property: against float64 on all rows
+    ref = util.bf16_to_f32(xb).reshape(n, n).astype(np.float64) @ util.bf16_to_f32(wb).reshape(n, n).astype(np.float64)
+    full_sabs = util.sum_abs_products(util.bf16_to_f32(xb).reshape(n, n), util.bf16_to_f32(wb).reshape(n, n))
+    assert util.acc_error(o.reshape(n, n), ref, full_sabs) <= util.ACC_TOL
+
+
+@pytest.mark.parametrize("bias", [7, 11])
+def test_config2_fp8_gemm_8192(calc, best_oracle, port, bias):
+    """Config 2: fp8_143 8192^3 -> bf16 RNE; bias 11 exercises the exponent-bias fold. Slice = a block
+    of A's rows against all of B."""
+    wl = dict(bench.WORKLOADS["fp8_gemm_8192"], bias=bias)
+    n = 8192
+    xb, wb = bench.synth_inputs(wl, seed=2)
+    kw = dict(fp_bias=bias, inf_nan_mode=abi.INFNAN_MINIMAL)
+    dx, dw, do = calc.to_device(xb), calc.to_device(wb), calc.alloc(n * n * 2)
+    calc.do_batch_gemm(T(do.ptr, abi.BF16, [n, n], mem_space=1), T(dx.ptr, abi.FP8_143, [n, n], mem_space=1, **kw),
+                       T(dw.ptr, abi.FP8_143, [n, n], mem_space=1, **kw), abi.OP_AB, abi.make_cast_params(abi.RM_NE))
+    calc.sync(20_000_000_000)
+    out = do.download(np.uint16).reshape(n, n)
+    rows = rows_for(best_oracle, n * n)
+    pick = np.sort(np.random.default_rng(3).choice(n, rows, replace=False))
+    xa = np.ascontiguousarray(xb.reshape(n, n)[pick])
+    acc = np.zeros(rows * n, np.float32)
+    assert best_oracle.bgemm(T(acc, abi.FP32, [n, rows]), T(xa, abi.FP8_143, [n, rows], **kw), T(wb, abi.FP8_143, [n, n], **kw), abi.OP_AB) == 0
+    ref = port.fp32_to_bf16(acc).reshape(rows, n)
+    sabs = util.sum_abs_products(util.decode(xa, abi.FP8_143, bias, 2, port).reshape(rows, n), util.decode(wb, abi.FP8_143, bias, 2, port).reshape(n, n))
+    inexact, far = util.check_rounded(out[pick], ref, 16, util.bf16_to_f32(out[pick]), util.bf16_to_f32(ref), sabs, "config 2")
+    assert inexact <= 0.01 * rows * n
+    # stochastic rounding (seeded Philox): every output is one of the two bf16 neighbours of the accumulator
+    calc.do_batch_gemm(T(do.ptr, abi.BF16, [n, n], mem_space=1), T(dx.ptr, abi.FP8_143, [n, n], mem_space=1, **kw),
+                       T(dw.ptr, abi.FP8_143, [n, n], mem_space=1, **kw), abi.OP_AB,
+                       abi.make_cast_params(abi.RM_SR, clip_fp=True, rng_kind=abi.RNG_PHILOX, rng_seed=5))
+    calc.sync(20_000_000_000)
+    sr = do.download(np.uint16).reshape(n, n)[pick]
+    lo = port.fp32_to_bf16(acc, abi.RM_Z).reshape(rows, n)
+    hi = port.fp32_to_bf16(acc, abi.RM_HAZ if False else abi.RM_Z).reshape(rows, n)
+    away = (lo.astype(np.int32) + 1).astype(np.uint16)
+    near = (sr == lo) | (sr == away) | (util.ulp_diff_bits(sr, ref, 16) <= 1)
+    d = np.abs(util.bf16_to_f32(sr).astype(np.float64) - acc.reshape(rows, n))
+    assert (near | (d <= util.ACC_TOL * sabs + np.abs(acc.reshape(rows, n)) * 2.0 ** -7)).all()
+    frac_up = (sr != lo).mean()
+    assert 0.3 < frac_up < 0.7  # discarded fractions are spread out: about half round up
+    for b in (dx, dw, do):
+        b.free()
+
+
+@pytest.mark.parametrize("opname", ["conv_fwd", "conv_dedx", "conv_dedw"])
+def test_config3_4_resnet_conv(calc, best_oracle, port, opname):
+    """Configs 3 and 4 at full size (64 x 56 x 56 x 256, 3x3, 256 -> 256). Slices: whole images for fwd /
+    dedx (first and last image), channel slices over the full N*H*W reduction for dedw."""
+    wl = bench.WORKLOADS[opname]
+    xs, ws, ys = bench.conv_shapes()
+    xb, wb, yb = bench.synth_inputs(wl, seed=3)
+    cp = abi.make_conv_params(2, (1, 1), (1, 1), (1, 1))
+    op = wl["op"]
+    oshape = {abi.OP_FWD: ys, abi.OP_DEDX: xs, abi.OP_DEDW: ws}[op]
+    n_out = int(np.prod(oshape))
+    dx, dw, dy = calc.to_device(xb), calc.to_device(wb), calc.to_device(yb)
+    do = calc.alloc(n_out * 4)
+    calc.do_convolution(T(do.ptr, abi.FP32, oshape, mem_space=1), T(dx.ptr, abi.BF16, xs, mem_space=1), T(dw.ptr, abi.BF16, ws, mem_space=1),
+                        T(dy.ptr, abi.BF16, ys, mem_space=1), cp, op)
+    calc.sync(20_000_000_000)
+    out = do.download(np.float32)
+    img_x, img_y = int(np.prod(xs[:3])), int(np.prod(ys[:3]))
+    if op in (abi.OP_FWD, abi.OP_DEDX):
+        # one whole image, restricted to a few output rows of the image to bound CPU time:
+        # crop H to 6 rows around the top border (padding included) -- the reduction per output is whole
+        Hc = 6
+        xs1, ys1 = [xs[0], xs[1], Hc + 1, 1], [ys[0], ys[1], Hc + 1, 1]
+        for img in (0, xs[3] - 1):
+            xi = xb[img * img_x: img * img_x + int(np.prod(xs1))]
+            yi = yb[img * img_y: img * img_y + int(np.prod(ys1))]
+            shp = ys1 if op == abi.OP_FWD else xs1
+            r = np.zeros(int(np.prod(shp)), np.float32)
+            assert best_oracle.conv(T(r, abi.FP32, shp), T(xi, abi.BF16, xs1), T(wb, abi.BF16, ws), T(yi, abi.BF16, ys1), cp, op) == 0
+            per_img = img_y if op == abi.OP_FWD else img_x
+            row = shp[0] * shp[1]
+            got = out[img * per_img: img * per_img + Hc * row]   # rows 0..Hc-1 see the same inputs as in the full image
+            want = r[:Hc * row]
+            assert np.abs(got - want).max() <= 2e-5 * np.abs(want).max(), (opname, img)
+    else:
+        # dedw: 8 input channels x 8 output channels, all taps, full reduction
+        cs, ks = 8, 8
+        x4 = xb.reshape(xs[3], xs[2], xs[1], xs[0])[..., :cs].copy()
+        y4 = yb.reshape(ys[3], ys[2], ys[1], ys[0])[..., :ks].copy()
+        shp = [ks, cs, 3, 3]
+        r = np.zeros(int(np.prod(shp)), np.float32)
+        assert best_oracle.conv(T(r, abi.FP32, shp), T(x4, abi.BF16, [cs, xs[1], xs[2], xs[3]]), T(np.zeros(int(np.prod(shp)), np.uint16), abi.BF16, shp),
+                                T(y4, abi.BF16, [ks, ys[1], ys[2], ys[3]]), cp, op) == 0
+        got = out.reshape(3, 3, ws[1], ws[0])[:, :, :cs, :ks]
+        want = r.reshape(3, 3, cs, ks)
+        # sum|ab| over 200704 terms of N(0,1) x N(0,0.01): about 200704 * 0.8 * 0.008
+        assert np.abs(got - want).max() <= util.ACC_TOL * 200704 * 0.8 * 0.008
+    for b in (dx, dw, dy, do):
+        b.free()
+
+
+def test_config5a_batched_attention_gemm(calc, best_oracle, port):
+    """Config 5a: 64 x ([4096 x 128] . [128 x 4096]^T-style abt) fp8_143 -> bf16. K = 128 sums of fp8
+    products are exact in fp32, so rounded outputs are compared bit for bit on sampled batches."""
+    wl = bench.WORKLOADS["fp8_bgemm_attn"]
+    B, M, N, K = 64, 4096, 4096, 128
+    xb, wb = bench.synth_inputs(wl, seed=5)
+    kw = dict(fp_bias=7, inf_nan_mode=abi.INFNAN_MINIMAL)
+    dx, dw, do = calc.to_device(xb), calc.to_device(wb), calc.alloc(B * M * N * 2)
+    calc.do_batch_gemm(T(do.ptr, abi.BF16, [N, M, B], mem_space=1), T(dx.ptr, abi.FP8_143, [K, M, B], mem_space=1, **kw),
+                       T(dw.ptr, abi.FP8_143, [K, N, B], mem_space=1, **kw), abi.OP_ABT, abi.make_cast_params(abi.RM_NE))
+    calc.sync(20_000_000_000)
+    out = do.download(np.uint16).reshape(B, M, N)
+    rows = 64
+    for b in (0, 37, 63):
+        xa = np.ascontiguousarray(xb.reshape(B, M, K)[b, 1000:1000 + rows])
+        wa = np.ascontiguousarray(wb.reshape(B, N, K)[b])
+        acc = np.zeros(rows * N, np.float32)
+        assert best_oracle.bgemm(T(acc, abi.FP32, [N, rows]), T(xa, abi.FP8_143, [K, rows], **kw), T(wa, abi.FP8_143, [K, N], **kw), abi.OP_ABT) == 0
+        ref = port.fp32_to_bf16(acc).reshape(rows, N)
+        assert (out[b, 1000:1000 + rows] == ref).mean() > 0.999
+        sabs = util.sum_abs_products(util.decode(xa, abi.FP8_143, 7, 2, port).reshape(rows, K), util.decode(wa, abi.FP8_143, 7, 2, port).reshape(N, K).T)
+        util.check_rounded(out[b, 1000:1000 + rows], ref, 16, util.bf16_to_f32(out[b, 1000:1000 + rows]), util.bf16_to_f32(ref), sabs, "config 5a")
+    for buf in (dx, dw, do):
+        buf.free()
+
+
+def test_config5b_mixed_fp8_mlp_projection(calc, best_oracle, port):
+    """Config 5b: fp8_152 activations [16384 x 8192] times fp8_143 weights [8192 x 28672] -> bf16."""
+    wl = bench.WORKLOADS["fp8_mlp"]
+    M, N, K = wl["M"], wl["N"], wl["K"]
+    xb, wb = bench.synth_inputs(wl, seed=6)
+    kx, kw_ = dict(fp_bias=15, inf_nan_mode=abi.INFNAN_FULL), dict(fp_bias=7, inf_nan_mode=abi.INFNAN_MINIMAL)
+    dx, dw, do = calc.to_device(xb), calc.to_device(wb), calc.alloc(M * N * 2)
+    calc.do_batch_gemm(T(do.ptr, abi.BF16, [N, M], mem_space=1), T(dx.ptr, abi.FP8_152, [K, M], mem_space=1, **kx),
+                       T(dw.ptr, abi.FP8_143, [N, K], mem_space=1, **kw_), abi.OP_AB, abi.make_cast_params(abi.RM_NE))
+    calc.sync(30_000_000_000)
+    rows = 8
+    pick = np.array([0, 1, 4095, 4096, 9999, 12345, 16382, 16383])
+    out = np.empty((rows, N), np.uint16)
+    full = do.download(np.uint16).reshape(M, N)
+    out[:] = full[pick]
+    del full
+    xa = np.ascontiguousarray(xb.reshape(M, K)[pick])
+    acc = np.zeros(rows * N, np.float32)
+    assert best_oracle.bgemm(T(acc, abi.FP32, [N, rows]), T(xa, abi.FP8_152, [K, rows], **kx), T(wb, abi.FP8_143, [N, K], **kw_), abi.OP_AB) == 0
+    ref = port.fp32_to_bf16(acc).reshape(rows, N)
+    sabs = util.sum_abs_products(util.decode(xa, abi.FP8_152, 15, 0, port).reshape(rows, K), util.decode(wb, abi.FP8_143, 7, 2, port).reshape(K, N))
+    inexact, far = util.check_rounded(out, ref, 16, util.bf16_to_f32(out), util.bf16_to_f32(ref), sabs, "config 5b")
+    assert inexact <= 0.01 * rows * N
+    for buf in (dx, dw, do):
+        buf.free()
+
+
+def test_full_size_properties_fp8_gemm(calc):
+    """Size-independent properties at config 2's full size: exact linearity under power-of-two scaling
+    (bias 7 vs bias 11 operands hold the same codes: outputs differ by exactly 2^-4 per operand), row
+    permutation invariance, and identity weights reproduce the input."""
+    n = 8192
+    wl = bench.WORKLOADS["fp8_gemm_8192"]
+    xb, wb = bench.synth_inputs(wl, seed=9)
+    dx, dw = calc.to_device(xb), calc.to_device(wb)
+    d1, d2 = calc.alloc(n * n * 4), calc.alloc(n * n * 4)
+
+    def gemm(dst, x_ptr, w_ptr, bx, bw):
+        calc.do_batch_gemm(T(dst.ptr, abi.FP32, [n, n], mem_space=1), T(x_ptr, abi.FP8_143, [n, n], mem_space=1, fp_bias=bx, inf_nan_mode=2),
+                           T(w_ptr, abi.FP8_143, [n, n], mem_space=1, fp_bias=bw, inf_nan_mode=2), abi.OP_AB)
+    gemm(d1, dx.ptr, dw.ptr, 7, 7)
+    gemm(d2, dx.ptr, dw.ptr, 11, 7)
+    calc.sync(20_000_000_000)
+    a, b = d1.download(np.float32), d2.download(np.float32)
+    assert (a == b * np.float32(16.0)).all()          # the bias fold is an exact power-of-two scale
+    # permuting rows of A permutes rows of C, bit for bit
+    perm = np.random.default_rng(1).permutation(n)
+    dxp = calc.to_device(np.ascontiguousarray(xb.reshape(n, n)[perm]))
+    gemm(d2, dxp.ptr, dw.ptr, 7, 7)
+    calc.sync(20_000_000_000)
+    assert (d2.download(np.float32).reshape(n, n).view(np.uint32) == a.reshape(n, n)[perm].view(np.uint32)).all()
+    # identity weights (1.0 = code 0x38 at bias 7): C == decode(A) exactly
+    eye = np.zeros((n, n), np.uint8)
+    np.fill_diagonal(eye, 0x38)
+    de = calc.to_device(eye)
+    gemm(d2, dx.ptr, de.ptr, 7, 7)
+    calc.sync(20_000_000_000)
+    from oracle import Port
+    assert (d2.download(np.float32) == Port().fp8_to_fp32(xb, 4, 7, 2)).all()
+    for buf in (dx, dw, d1, d2, dxp, de):
+        buf.free()

@@ -1,0 +1,108 @@
+"""The product's conversion functions (csrc/numerics.cuh) compiled for the host and compared, bit for
+bit, with the CPU oracle. This checks the device code's arithmetic on a machine without a GPU; the
+GPU tests repeat the comparison through the kernels."""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from intel_gaudi3_software_b200 import abi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+SRC = os.path.join(ROOT, "tests", "hostcheck", "numerics_host.cpp")
+SO = os.path.join(ROOT, "tests", "hostcheck", "libnumerics_host.so")
+
+
+@pytest.fixture(scope="module")
+def hc():
+    inc = os.path.join(ROOT, "intel_gaudi3_software_b200", "csrc")
+    if not os.path.exists(SO) or os.path.getmtime(SO) < max(os.path.getmtime(SRC), os.path.getmtime(os.path.join(inc, "numerics.cuh"))):
+        subprocess.check_call(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-I" + inc, "-o", SO, SRC])
+    return C.CDLL(SO)
+
+
+def inputs():
+    rng = np.random.default_rng(11)
+    n = 40000
+    bits = rng.integers(0, 2**32, size=n, dtype=np.uint64).astype(np.uint32)
+    ex = rng.integers(127 - 40, 127 + 20, size=n).astype(np.uint32)
+    b2 = (bits & 0x807FFFFF) | (ex << 23)
+    special = np.array([0, 0x80000000, 0x7F800000, 0xFF800000, 0x7FC00000, 0xFFC00001, 1, 0x80000001, 0x007FFFFF,
+                        0x7F7FFFFF, 0xFF7FFFFF], dtype=np.uint32)
+    allbits = np.concatenate([bits, b2, b2 & 0xFFF00000, b2 & 0xFFF80000, special])
+    lfsr = rng.integers(0, 2**32, size=allbits.size, dtype=np.uint64).astype(np.uint32)
+    lfsr[:300] = 0
+    return allbits, lfsr
+
+
+def test_decode(hc, port):
+    codes = np.arange(256, dtype=np.uint8)
+    out = np.zeros(256, np.uint32)
+    for ew, biases in ((4, (3, 7, 11, 15)), (5, (1, 15, 30))):
+        for b in biases:
+            for mode in (0, 1, 2):
+                hc.hc_fp8_decode(codes.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p), C.c_size_t(256), ew, b, mode)
+                assert (out == port.fp8_to_fp32(codes, ew, b, mode).view(np.uint32)).all()
+
+
+def test_casts(hc, port):
+    bits, lfsr = inputs()
+    n = bits.size
+
+    def run(out_dtype, ew, bias, mode, rm, relu, clip, cii, ftz, sftz):
+        out = np.zeros(n * abi.ELEM_SIZE[out_dtype], np.uint8)
+        hc.hc_cast(bits.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p), C.c_size_t(n), out_dtype, ew, bias, mode, rm,
+                   relu, clip, cii, ftz, sftz, lfsr.ctypes.data_as(C.c_void_p))
+        return out
+    for rm in (0, 1, 2, 3, 4, 6, 7):
+        for clip, ftz, cii in ((0, 0, 0), (1, 0, 0), (1, 1, 1), (0, 1, 0)):
+            got = run(abi.BF16, 0, 0, 0, rm, 0, clip, cii, ftz, 0).view(np.uint16)
+            assert (got == port.fp32_to_bf16(bits, rm, lfsr, clip, ftz, cii)).all(), (rm, clip, ftz, cii)
+        for dt, ew, b, mode in ((abi.FP8_143, 4, 3, 0), (abi.FP8_143, 4, 7, 2), (abi.FP8_143, 4, 11, 1), (abi.FP8_152, 5, 15, 0), (abi.FP8_152, 5, 30, 2)):
+            for ftz, clip, cii, sftz in ((0, 0, 0, 0), (1, 0, 0, 0), (0, 1, 1, 0), (1, 1, 0, 1), (0, 0, 0, 1)):
+                got = run(dt, ew, b, mode, rm, 0, clip, cii, ftz, sftz)
+                assert (got == port.fp32_to_fp8(bits, ew, b, rm, lfsr, ftz, clip, cii, sftz, mode)).all(), (dt, b, mode, rm, ftz, clip, cii, sftz)
+
+
+def test_foreign_code_predicate(hc, port):
+    """A code is 'foreign' exactly when the reference decode differs from the tensor cores' decode
+    (OCP E4M3 = the 1-4-3 'minimal' convention at bias 7; OCP E5M2 = the 1-5-2 'full' convention at bias 15)."""
+    codes = np.arange(256, dtype=np.uint8)
+    for ew, hw_bias, hw_mode in ((4, 7, 2), (5, 15, 0)):
+        hw = port.fp8_to_fp32(codes, ew, hw_bias, hw_mode).view(np.uint32)
+        for mode in (0, 1, 2):
+            mine = port.fp8_to_fp32(codes, ew, hw_bias, mode).view(np.uint32)
+            for c in range(256):
+                assert bool(hc.hc_fp8_foreign(c, ew, mode)) == bool(hw[c] != mine[c]), (ew, mode, c)
+
+
+def test_lfsr_step(hc, port):
+    hc.hc_lfsr.restype = C.c_uint32
+    v = 0xDEADBEEF
+    for _ in range(200):
+        nxt = hc.hc_lfsr(C.c_uint32(v), C.c_uint32(37))
+        assert nxt == port.lfsr32(v, 37)
+        v = nxt
+
+
+def test_philox_known_answers(hc):
+    """Philox4x32-10 known-answer vectors of the Random123 distribution (kat_vectors)."""
+    def block(ctr, key):
+        c = (C.c_uint32 * 4)(*ctr)
+        hc.hc_philox_block(c, C.c_uint32(key[0]), C.c_uint32(key[1]))
+        return list(c)
+    assert block([0, 0, 0, 0], [0, 0]) == [0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8]
+    assert block([0xFFFFFFFF] * 4, [0xFFFFFFFF, 0xFFFFFFFF]) == [0x408F276D, 0x41C83B0E, 0xA20BC7C6, 0x6D5451FD]
+    assert block([0x243F6A88, 0x85A308D3, 0x13198A2E, 0x03707344], [0xA4093822, 0x299F31D0]) == [0xD16CFE09, 0x94FDCCEB, 0x5001E420, 0x24126EA1]
+
+
+def test_philox_word_never_zero_and_uniform(hc):
+    hc.hc_philox.restype = C.c_uint32
+    w = np.array([hc.hc_philox(C.c_uint64(5), C.c_uint64(0), C.c_uint64(i)) for i in range(20000)], dtype=np.uint64)
+    assert (w != 0).all()
+    # top bit and a middle bit are fair coins (5 sigma)
+    for bit in (31, 13):
+        ones = int(((w >> bit) & 1).sum())
+        assert abs(ones - 10000) < 5 * 71
