@@ -80,7 +80,7 @@ class ClockSampler:
         self.proc = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                          "--format=csv,noheader,nounits", "-lms", "20"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
         except OSError:
             pass
@@ -366,7 +366,7 @@ def run_ours(args):
                      "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_note": note,
                      "algorithmic_flops_per_launch": flops, "algorithmic_bytes_per_launch": alg_bytes},
     }
-    if world == 1:
+    if world == 1 and not args.skip_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(wl, args.workload, budget_s=12.0)
     print(json.dumps(line))
 
@@ -474,10 +474,11 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="fp8_gemm_8192", choices=sorted(WORKLOADS))
+    ap.add_argument("--skip-cpu-baseline", action="store_true", help="leave the CPU baseline leg out (sweeps)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
