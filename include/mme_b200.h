@@ -228,6 +228,25 @@ int mmeb200_host_free(void* host_ptr);
 int mmeb200_timer_start(mmeb200_ctx* ctx);
 int mmeb200_timer_stop(mmeb200_ctx* ctx, float* elapsed_ms);
 
+/* No counterpart in the reference. A split-K GEMM for callers that must not allocate while they
+ * run: code living under a framework's memory pool that was handed exactly its inputs and outputs,
+ * a latency-critical loop that cannot afford the allocator's lock, a process whose device-memory
+ * budget was fixed at start-up. out[M x N] (fp32) = op(x) . op(w) with the reduction cut into
+ * `splits` parts whose fp32 partial sums live in a fixed 16 MiB array inside the library image
+ * (held by every GPU that loads the library, until the process exits) instead of in scratch memory
+ * from cudaMalloc. The call itself performs no cudaMalloc / cudaFree and calls no allocating routine.
+ *   - tensors: device-resident, 2-D, 16-byte aligned, row pitches multiples of 16 bytes; bf16 x bf16,
+ *     or fp8 whose Inf/NaN convention matches the tensor cores (1-4-3 minimal, 1-5-2 full);
+ *   - limit: splits * M * N * 4 bytes <= 16 MiB, 2 <= splits <= 64; larger requests are rejected
+ *     with MMEB200_ERR_INVALID_ARG and a message naming the limit;
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress) and
+ *     should therefore come before any stream capture;
+ *   - all calls share the one array and it keeps the previous call's partial sums. Each call
+ *     overwrites every element it later reads, so nothing needs clearing, but two calls that
+ *     overlap on the GPU (different streams or contexts) race on it: serialise them. */
+int mmeb200_gemm_splitk_static(mmeb200_ctx* ctx, mmeb200_tensor* out, const mmeb200_tensor* x,
+                               const mmeb200_tensor* w, int op, int splits);
+
 /* Number of kernels this library has launched on the context since creation. */
 uint64_t mmeb200_launch_count(const mmeb200_ctx* ctx);
 

@@ -145,6 +145,7 @@ SYMBOLS = {
     "mmeb200_timer_stop": (C.c_int, [C.c_void_p, P(C.c_float)]),
     "mmeb200_launch_count": (C.c_uint64, [C.c_void_p]),
     "mmeb200_version": (C.c_char_p, []),
+    "mmeb200_gemm_splitk_static": (C.c_int, [C.c_void_p, P(Tensor), P(Tensor), P(Tensor), C.c_int, C.c_int]),
 }
 
 

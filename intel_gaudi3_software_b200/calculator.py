@@ -101,6 +101,11 @@ class Calculator:
     def convert(self, out, inp, cast=None):
         self._check(self.lib.mmeb200_convert(self.ctx, out, inp, cast))
 
+    def gemm_splitk_static(self, out, x, w, op, splits):
+        """Split-K GEMM whose partial sums live in the library's fixed 16 MiB device array: for callers
+        that may not allocate (see include/mme_b200.h). Device tensors only."""
+        self._check(self.lib.mmeb200_gemm_splitk_static(self.ctx, out, x, w, op, splits))
+
     # ---- state and plumbing -----------------------------------------------------------------
     def get_lfsr(self, n=256):
         regs = np.zeros(n, dtype=np.uint32)

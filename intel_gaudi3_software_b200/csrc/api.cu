@@ -1256,3 +1256,116 @@ int mmeb200_dma(mmeb200_ctx* c, mmeb200_tensor* out, const mmeb200_tensor* x, in
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------ split-K GEMM without allocations
+// The split-K path above keeps its fp32 partial sums in scratch memory that the context obtains
+// with cudaMalloc on demand. Some callers may not allocate at the moment they need a GEMM: code
+// that runs under a framework's memory pool and has been handed exactly its inputs and outputs, a
+// latency-critical loop that must not hit the allocator's lock, or a process whose memory budget
+// was fixed at start-up. For them the same kernels run with the partial sums in the fixed array
+// below, which is part of the library image: every GPU that loads the library holds these 16 MiB
+// until the process exits.
+constexpr size_t kStaticSplitKBytes = size_t(16) << 20;
+static __device__ __align__(256) unsigned char g_static_splitk_ws[kStaticSplitKBytes];
+// Device address of g_static_splitk_ws per CUDA ordinal. In host code the array's name is only a
+// handle for the runtime, never an address a kernel may use; cudaGetSymbolAddress translates it.
+static void* g_static_splitk_addr[64] = {};
+
+extern "C" int mmeb200_gemm_splitk_static(mmeb200_ctx* c, mmeb200_tensor* out, const mmeb200_tensor* x, const mmeb200_tensor* w,
+                                          int op, int splits) {
+    if (!c) return MMEB200_ERR_INVALID_ARG;
+    cudaSetDevice(c->device);
+    TRY(check_tensor(c, out, "output"));
+    TRY(check_tensor(c, x, "x"));
+    TRY(check_tensor(c, w, "w"));
+    if (op < MMEB200_OP_AB || op > MMEB200_OP_ATBT) return c->fail(MMEB200_ERR_INVALID_ARG, "operation %d is not a gemm operation", op);
+    if (out->mem_space != MMEB200_MEM_DEVICE || x->mem_space != MMEB200_MEM_DEVICE || w->mem_space != MMEB200_MEM_DEVICE)
+        return c->fail(MMEB200_ERR_INVALID_ARG, "the allocation-free gemm takes device-resident tensors only (staging host tensors would allocate)");
+    if (out->dtype != DT_FP32) return c->fail(MMEB200_ERR_INVALID_ARG, "the allocation-free gemm writes the fp32 accumulator");
+    for (int d = 2; d < 5; ++d)
+        if (out->sizes[d] != 1 || x->sizes[d] != 1 || w->sizes[d] != 1) return c->fail(MMEB200_ERR_UNSUPPORTED, "the allocation-free gemm is 2-D (no batch dims)");
+    const bool x8 = dtype_is_fp8(x->dtype), w8 = dtype_is_fp8(w->dtype);
+    auto native8 = [](const mmeb200_tensor* t) { return (t->dtype == DT_FP8_143 && t->inf_nan_mode == 2) || (t->dtype == DT_FP8_152 && t->inf_nan_mode == 0); };
+    if (!((x->dtype == DT_BF16 && w->dtype == DT_BF16) || (x8 && w8 && native8(x) && native8(w))))
+        return c->fail(MMEB200_ERR_UNSUPPORTED, "the allocation-free gemm takes bf16 x bf16, or fp8 operands whose Inf/NaN convention the tensor cores share "
+                                                "(1-4-3 'minimal', 1-5-2 'full'); other formats need converted copies, i.e. scratch allocations");
+    const bool tA = (op == MMEB200_OP_ATB || op == MMEB200_OP_ATBT), tB = (op == MMEB200_OP_ABT || op == MMEB200_OP_ATBT);
+    const uint64_t M = tA ? x->sizes[0] : x->sizes[1], K = tA ? x->sizes[1] : x->sizes[0];
+    const uint64_t Kb = tB ? w->sizes[0] : w->sizes[1], N = tB ? w->sizes[1] : w->sizes[0];
+    if (M == 0 || N == 0 || K == 0) return c->fail(MMEB200_ERR_INVALID_ARG, "empty operands");
+    if (K != Kb) return c->fail(MMEB200_ERR_INVALID_ARG, "Common dim doesnt match between input A\\B");
+    if (out->sizes[0] != N || out->sizes[1] != M) return c->fail(MMEB200_ERR_INVALID_ARG, "output width doesnt match to inputB width");
+    const int elem = dtype_size(x->dtype);
+    const uint32_t block_k = kRowBytes / elem;
+    const uint32_t num_k_blocks = uint32_t((K + block_k - 1) / block_k);
+    if (splits < 2 || splits > 64 || uint32_t(splits) > num_k_blocks)
+        return c->fail(MMEB200_ERR_INVALID_ARG, "splits must be in [2, min(64, %u k-blocks)], got %d", num_k_blocks, splits);
+    if (((num_k_blocks + splits - 1) / splits) * uint32_t(splits - 1) >= num_k_blocks)
+        return c->fail(MMEB200_ERR_INVALID_ARG, "%d splits of %u k-blocks would leave a split empty", splits, num_k_blocks);
+    const uint64_t need = uint64_t(splits) * M * N * 4;
+    if (need > kStaticSplitKBytes)
+        return c->fail(MMEB200_ERR_INVALID_ARG, "splits * M * N * 4 = %llu bytes exceeds the fixed %llu-byte workspace of the allocation-free gemm",
+                       (unsigned long long) need, (unsigned long long) kStaticSplitKBytes);
+
+    // one-time set-up per device: translate the symbol to its device address (this device is current)
+    if (c->device < 0 || c->device >= 64) return c->fail(MMEB200_ERR_INVALID_ARG, "device ordinal %d out of range", c->device);
+    if (!g_static_splitk_addr[c->device]) {
+        void* addr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&addr, g_static_splitk_ws);
+        if (e != cudaSuccess || !addr) return c->fail(MMEB200_ERR_CUDA, "cudaGetSymbolAddress(static split-K workspace): %s", cudaGetErrorString(e));
+        g_static_splitk_addr[c->device] = addr;
+    }
+    void* ws = g_static_splitk_addr[c->device];
+
+    LogicalOperand la, lb;
+    la.ptr = x->data; la.dtype = x->dtype; la.bias = int(x->fp_bias); la.mode = x->inf_nan_mode;
+    la.mn = M; la.k = K; la.mn_stride = tA ? 1 : x->strides[1]; la.k_stride = tA ? x->strides[1] : 1;
+    lb.ptr = w->data; lb.dtype = w->dtype; lb.bias = int(w->fp_bias); lb.mode = w->inf_nan_mode;
+    lb.mn = N; lb.k = K; lb.mn_stride = tB ? w->strides[1] : 1; lb.k_stride = tB ? 1 : w->strides[1];
+    for (int i = 0; i < 3; ++i) { la.bsz[i] = lb.bsz[i] = 1; la.bstride[i] = lb.bstride[i] = 0; }
+    TmaOperand a, b;
+    if (native_operand(la, &a) != 0 || !tma_compatible(a) || native_operand(lb, &b) != 0 || !tma_compatible(b))
+        return c->fail(MMEB200_ERR_UNSUPPORTED, "operands must be 16-byte aligned with row pitches that are multiples of 16 bytes "
+                                                "(anything else needs a repacked copy, i.e. a scratch allocation)");
+    float scale = 1.0f;
+    uint32_t kind = KIND_F16;
+    if (x8) {
+        kind = KIND_F8;
+        a.hw_fmt = x->dtype == DT_FP8_143 ? 0 : 1;
+        b.hw_fmt = w->dtype == DT_FP8_143 ? 0 : 1;
+        scale = ldexpf(1.0f, ((x->dtype == DT_FP8_143 ? 7 : 15) - int(x->fp_bias)) + ((w->dtype == DT_FP8_143 ? 7 : 15) - int(w->fp_bias)));
+    } else {
+        a.hw_fmt = b.hw_fmt = 1;
+    }
+
+    GemmParams p;
+    memset(&p, 0, sizeof p);
+    p.M = uint32_t(M); p.N = uint32_t(N); p.K = uint32_t(K);
+    p.elem_bytes = elem; p.block_k = block_k; p.num_k_blocks = num_k_blocks;
+    p.m_tiles = uint32_t((M + kBlockM - 1) / kBlockM);
+    p.batches = 1;
+    for (int i = 0; i < 3; ++i) { p.bsz[i] = 1; p.a_bcast[i] = 1; p.b_bcast[i] = 1; }
+    p.a_mn_major = a.mn_major; p.b_mn_major = b.mn_major; p.a_mode = A_TILED;
+    constexpr int block_n = 128;
+    p.n_tiles = uint32_t((N + block_n - 1) / block_n);
+    p.split_k = uint32_t(splits);
+    p.idesc = make_instr_desc(a.hw_fmt, b.hw_fmt, a.mn_major, b.mn_major, kBlockM, block_n);
+    p.status = c->d_status;
+    p.scale = 1.0f; p.out_dtype = DT_FP32; p.has_cast = 0; p.epi_mode = EPI_F32;
+    p.out = ws;   // every (split, tile) overwrites its whole region of the workspace: nothing has to start at zero
+    TRY(encode_tiled(c, &p.tm_a, a, a.mn_major ? kRowBytes / elem : block_k, a.mn_major ? block_k : kBlockM));
+    TRY(encode_tiled(c, &p.tm_b, b, b.mn_major ? kRowBytes / elem : block_k, b.mn_major ? block_k : block_n));
+    const uint64_t tiles = uint64_t(p.m_tiles) * p.n_tiles * splits;
+    const unsigned grid = unsigned(std::min<uint64_t>(tiles, uint64_t(c->sm_count)));
+    const int launch_rc = (kind == KIND_F16) ? launch_gemm_kernel<KIND_F16, 128, 6>(c, p, grid) : launch_gemm_kernel<KIND_F8, 128, 6>(c, p, grid);
+    TRY(launch_rc);
+    ReduceOut r;
+    memset(&r, 0, sizeof r);
+    r.out = out->data; r.out_dtype = DT_FP32; r.has_cast = 0; r.out_ld = out->strides[1];
+    for (int i = 0; i < 3; ++i) r.bsz[i] = 1;
+    r.M = p.M; r.N = p.N; r.batches = 1; r.splits = uint32_t(splits); r.scale = scale;
+    splitk_reduce_kernel<<<grid_for(M * N, 256, c->sm_count), 256, 0, c->stream>>>(static_cast<const float*>(ws), r);
+    c->launches++;
+    CUDA_OK(c, cudaGetLastError());
+    return 0;
+}
