@@ -228,7 +228,7 @@ static bool tma_compatible(const TmaOperand& o) {
     return true;
 }
 
-static int encode_tiled(mmeb200_ctx* c, CUtensorMap* tm, const TmaOperand& o, uint32_t box_inner, uint32_t box_rows) {
+static int encode_tiled(mmeb200_ctx* c, CUtensorMap* tm, const TmaOperand& o, uint32_t box_inner, uint32_t box_rows, int u16_type = 0) {
     TRY(load_driver_entry_points(c));
     cuuint64_t dims[5] = {o.inner, o.rows, o.bsz[0], o.bsz[1], o.bsz[2]};
     cuuint64_t strides[4];
@@ -242,7 +242,9 @@ static int encode_tiled(mmeb200_ctx* c, CUtensorMap* tm, const TmaOperand& o, ui
     }
     cuuint32_t box[5] = {box_inner, box_rows, 1, 1, 1};
     cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-    CUresult r = g_encode_tiled(tm, tma_dtype(o.elem), 5, const_cast<void*>(o.ptr), dims, strides, box, estr,
+    // 16-bit outputs are raw bit patterns: describe them as integers so the copy engine cannot touch them
+    const CUtensorMapDataType dt = (u16_type == 2) ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : tma_dtype(o.elem);
+    CUresult r = g_encode_tiled(tm, dt, 5, const_cast<void*>(o.ptr), dims, strides, box, estr,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
@@ -311,16 +313,18 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     p.b_mn_major = j.b.mn_major;
     p.a_mode = j.a_im2col ? A_IM2COL : A_TILED;
     p.conv = j.conv;
-    // tile width: 256 when that still fills the machine, else 128
-    const uint32_t n256 = (j.N + 255) / 256;
-    const bool wide = j.N > 128 && uint64_t(p.m_tiles) * n256 * p.batches >= uint64_t(c->sm_count);
-    const int block_n = wide ? 256 : 128;
+    // tile width: 256 columns whenever the problem has them (half the operand traffic per FLOP of a
+    // 128-wide tile); split-K below fills the machine when that leaves few tiles
+    const bool wide = j.N > 128;
+    int block_n = wide ? 256 : 128;
+    if (const char* e = getenv("MME_B200_BLOCK_N")) block_n = atoi(e) == 256 ? 256 : 128;   // tuning knob
     p.n_tiles = (j.N + block_n - 1) / block_n;
     const uint64_t tiles = uint64_t(p.m_tiles) * p.n_tiles * p.batches;
     uint32_t split = 1;
-    if (j.force_split > 0) split = j.force_split;
-    else if (tiles * 2 <= uint64_t(c->sm_count) && p.num_k_blocks >= 16) {
-        split = uint32_t(std::min<uint64_t>(c->sm_count / tiles, p.num_k_blocks / 8));
+    if (const char* e = getenv("MME_B200_SPLIT_K")) j.force_split = atoi(e);                   // tuning knob
+    if (j.force_split > 0) split = std::min<uint32_t>(j.force_split, p.num_k_blocks);
+    else if (tiles * 2 <= uint64_t(c->sm_count) && p.num_k_blocks >= 8) {
+        split = uint32_t(std::min<uint64_t>(c->sm_count / tiles, p.num_k_blocks / 4));
         split = std::max(1u, std::min(split, 64u));
     }
     // no empty splits
@@ -351,6 +355,13 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     else TRY(encode_tiled(c, &p.tm_a, j.a, kRowBytes / elem, p.block_k));
     if (!j.b.mn_major) TRY(encode_tiled(c, &p.tm_b, j.b, p.block_k, block_n));
     else TRY(encode_tiled(c, &p.tm_b, j.b, kRowBytes / elem, p.block_k));
+    // coalesced TMA stores when the output's base and pitches allow a tensor map
+    if (split == 1 && !getenv("MME_B200_NO_TMA_STORE")) {
+        TmaOperand od;
+        od.ptr = o.ptr; od.elem = dtype_size(o.dtype); od.mn_major = false; od.inner = j.N; od.rows = j.M; od.row_stride = o.ld;
+        for (int i = 0; i < 3; ++i) { od.bsz[i] = j.bsz[i]; od.bstride[i] = o.bstride[i]; }
+        if ((uint64_t(j.N) * od.elem) % 16 == 0 && tma_compatible(od) && encode_tiled(c, &p.tm_out, od, kRowBytes / od.elem, kBlockM, od.elem == 2 ? 2 : 0) == 0) p.tma_store = 1;
+    }
 
     const unsigned grid = unsigned(std::min<uint64_t>(tiles * split, uint64_t(c->sm_count)));
     int rc;

@@ -13,7 +13,9 @@
 //               the accumulator.
 //   warp 2      allocates and frees tensor memory.
 //   warps 4-7   epilogue: tcgen05.ld the accumulator (lane = row), scale, optional ReLU + rounded
-//               cast, store. Runs concurrently with the next tile's main loop.
+//               cast, then either stage 128-byte column chunks in shared memory for TMA stores
+//               (aligned outputs) or store directly (unaligned outputs, split-K partials).
+//               Runs concurrently with the next tile's main loop.
 // Tiles are walked in a grouped raster so that concurrently resident CTAs share operand panels
 // in L2. Every mbarrier wait is bounded; a wait that gives up writes a code to p.status and the
 // CTA leaves through the normal teardown.
@@ -58,6 +60,8 @@ struct ConvGeom {
 struct GemmParams {
     CUtensorMap tm_a;
     CUtensorMap tm_b;
+    CUtensorMap tm_out;      // output as (N, M, b0, b1, b2), box 128 B x 128 rows; used when tma_store != 0
+    uint32_t tma_store;
     uint32_t M, N, K;
     uint32_t block_k;       // elements per k block (128 B / element size)
     uint32_t num_k_blocks;  // over the whole K
@@ -88,8 +92,9 @@ struct GemmSmem {
     static constexpr int kABytes = kBlockM * kRowBytes;
     static constexpr int kBBytes = BLOCK_N * kRowBytes;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kBarrierBytes = 256;
-    static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + 1024 /* alignment slack */;
+    static constexpr int kBarrierBytes = 1024;   // keeps the output staging buffers 1024-byte aligned
+    static constexpr int kOutStageBytes = 2 * kBlockM * kRowBytes;
+    static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + kOutStageBytes + 1024 /* alignment slack */;
 };
 
 struct TileCoord {
@@ -114,6 +119,46 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, uint32_t t
     c.kb_begin = c.split * per_split;
     c.kb_end = min(p.num_k_blocks, c.kb_begin + per_split);
     return c;
+}
+
+// Turns 32 fp32 accumulator columns into 32 outputs of the launch's output type, packed little-endian
+// into the first 8 * out_elem words of v: scale, NaN canonicalisation, optional ReLU, rounded cast.
+__device__ __forceinline__ void epilogue_convert(uint32_t (&v)[32], const GemmParams& p, uint32_t out_elem, uint64_t flat_index) {
+    if (p.epi_mode == EPI_BF16_RNE) {
+        // round-to-nearest-even with no flags: the hardware conversion gives the reference's bits
+        // (NaN -> 0x7FFF, denormals kept)
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float lo = __uint_as_float(v[2 * j]) * p.scale, hi = __uint_as_float(v[2 * j + 1]) * p.scale;
+            uint32_t packed;
+            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
+            v[j] = packed;
+        }
+    } else if (p.epi_mode == EPI_F32) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const uint32_t bits = __float_as_uint(__uint_as_float(v[j]) * p.scale);
+            v[j] = f32_is_nan(bits) ? kF32CanonNan : bits;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            uint32_t bits = __float_as_uint(__uint_as_float(v[j]) * p.scale);
+            if (f32_is_nan(bits)) bits = kF32CanonNan;
+            if (p.cast.relu) bits = relu_bits(bits);
+            uint32_t rnd = 0;
+            if (p.rng_philox) rnd = philox_word(p.rng_seed, p.rng_offset, flat_index + j);
+            v[j] = cast_from_f32(bits, p.cast, rnd);
+        }
+        if (out_elem == 2) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = (v[2 * j] & 0xFFFFu) | (v[2 * j + 1] << 16);
+        } else if (out_elem == 1) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                v[j] = (v[4 * j] & 0xFFu) | ((v[4 * j + 1] & 0xFFu) << 8) | ((v[4 * j + 2] & 0xFFu) << 16) | (v[4 * j + 3] << 24);
+        }
+    }
 }
 
 template <int KIND, int BLOCK_N, int STAGES>
@@ -143,6 +188,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
         fence_mbar_init();
         tma_prefetch_desc(&p.tm_a);
         tma_prefetch_desc(&p.tm_b);
+        if (p.tma_store) tma_prefetch_desc(&p.tm_out);
     }
     if (warp == 2) {
         tmem_alloc(tmem_holder, 2 * BLOCK_N);
@@ -155,13 +201,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
+        // One thread feeds the ring. Everything that does not change inside a tile is computed
+        // before the k loop, and coordinates advance incrementally: no division per k block.
         if (elect_one()) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            const uint32_t a_groups = p.a_mn_major ? (kBlockM * p.elem_bytes) / kRowBytes : 1;
-            const uint32_t b_groups = p.b_mn_major ? (BLOCK_N * p.elem_bytes) / kRowBytes : 1;
+            const bool a_mn = p.a_mn_major != 0, b_mn = p.b_mn_major != 0;
+            const bool im2col = p.a_mode == A_IM2COL;
+            const bool pix_k = im2col && p.conv.pixels_along_k;
+            const uint32_t a_groups = a_mn ? (kBlockM * p.elem_bytes) / kRowBytes : 1;   // <= 4
+            const uint32_t b_groups = b_mn ? (BLOCK_N * p.elem_bytes) / kRowBytes : 1;   // <= 8
             const uint32_t mn_group_elems = kRowBytes / p.elem_bytes;
             const uint32_t mn_group_bytes = p.block_k * kRowBytes;
+            const uint32_t block_k = p.block_k;
             for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const TileCoord tc = decode_tile(p, t);
                 const uint32_t n0 = tc.n0 * BLOCK_N;
@@ -172,14 +224,41 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
                     bi[1] = b % p.bsz[1]; b /= p.bsz[1];
                     bi[2] = b;
                 }
-                // im2col: base position of the tile's first pixel (fwd / dedx)
-                int pw = 0, ph = 0, pn = 0;
-                if (p.a_mode == A_IM2COL && !p.conv.pixels_along_k) {
+                const int ab0 = p.a_bcast[0] ? 0 : bi[0], ab1 = p.a_bcast[1] ? 0 : bi[1], ab2 = p.a_bcast[2] ? 0 : bi[2];
+                const int bb0 = p.b_bcast[0] ? 0 : bi[0], bb1 = p.b_bcast[1] ? 0 : bi[1], bb2 = p.b_bcast[2] ? 0 : bi[2];
+                uint32_t k_elem = tc.kb_begin * block_k;   // K coordinate of plain (tiled) operands
+                // ---- per-tile im2col state
+                int pw = 0, ph = 0, pn = 0;                // base position of the tile's first pixel (fwd / dedx)
+                uint32_t tap_s = 0, tap_r = 0, k_in_tap = 0, tap = 0;   // fwd / dedx: filter tap and channel offset
+                uint32_t pq = 0, pp = 0, pimg = 0;         // dedw: pixel position of the k block
+                uint16_t g_off_w[4] = {0, 0, 0, 0}, g_off_h[4] = {0, 0, 0, 0};
+                int g_c[4] = {0, 0, 0, 0};
+                if (im2col && !pix_k) {
                     const uint32_t q = tc.m0 % p.conv.out_w;
                     const uint32_t rest = tc.m0 / p.conv.out_w;
                     pw = int(q) * p.conv.stride_w + p.conv.lower_w;
                     ph = int(rest % p.conv.out_h) * p.conv.stride_h + p.conv.lower_h;
                     pn = int(rest / p.conv.out_h);
+                    tap = tc.kb_begin / p.conv.k_blocks_per_tap;
+                    k_in_tap = (tc.kb_begin % p.conv.k_blocks_per_tap) * block_k;
+                    tap_s = tap % p.conv.taps_w;
+                    tap_r = tap / p.conv.taps_w;
+                } else if (pix_k) {
+                    const uint32_t pix = tc.kb_begin * block_k;
+                    pq = pix % p.conv.out_w;
+                    const uint32_t rest = pix / p.conv.out_w;
+                    pp = rest % p.conv.out_h;
+                    pimg = rest / p.conv.out_h;
+#pragma unroll
+                    for (uint32_t g = 0; g < 4; ++g) {
+                        if (g < a_groups) {
+                            const uint32_t m = tc.m0 + g * mn_group_elems;
+                            const uint32_t tp = m / p.conv.channels;
+                            g_c[g] = int(m % p.conv.channels);
+                            g_off_w[g] = uint16_t((tp % p.conv.taps_w) * p.conv.dil_w);
+                            g_off_h[g] = uint16_t((tp / p.conv.taps_w) * p.conv.dil_h);
+                        }
+                    }
                 }
                 for (uint32_t kb = tc.kb_begin; kb < tc.kb_end; ++kb) {
                     if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, kWaitLimitNs)) {
@@ -189,55 +268,56 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
                     }
                     uint8_t* a_dst = smem + stage * S::kStageBytes;
                     uint8_t* b_dst = a_dst + S::kABytes;
-                    mbar_arrive_expect_tx(&full_bar[stage], S::kStageBytes);
-                    uint32_t k_elem = kb * p.block_k;  // K coordinate for plain operands
-                    uint32_t tap = 0, k_in_tap = k_elem;
-                    if (p.a_mode == A_IM2COL && !p.conv.pixels_along_k) {
-                        tap = kb / p.conv.k_blocks_per_tap;
-                        k_in_tap = (kb % p.conv.k_blocks_per_tap) * p.block_k;
-                    }
+                    uint64_t* bar = &full_bar[stage];
+                    mbar_arrive_expect_tx(bar, S::kStageBytes);
                     // ---- A
-                    if (p.a_mode == A_TILED) {
-                        const int b0 = p.a_bcast[0] ? 0 : bi[0], b1 = p.a_bcast[1] ? 0 : bi[1], b2 = p.a_bcast[2] ? 0 : bi[2];
-                        if (!p.a_mn_major) {
-                            tma_load_5d(a_dst, &p.tm_a, &full_bar[stage], k_elem, tc.m0, b0, b1, b2);
+                    if (!im2col) {
+                        if (!a_mn) {
+                            tma_load_5d(a_dst, &p.tm_a, bar, k_elem, tc.m0, ab0, ab1, ab2);
                         } else {
-                            for (uint32_t g = 0; g < a_groups; ++g)
-                                tma_load_5d(a_dst + g * mn_group_bytes, &p.tm_a, &full_bar[stage],
-                                            tc.m0 + g * mn_group_elems, k_elem, b0, b1, b2);
+#pragma unroll
+                            for (uint32_t g = 0; g < 4; ++g)
+                                if (g < a_groups)
+                                    tma_load_5d(a_dst + g * mn_group_bytes, &p.tm_a, bar, tc.m0 + g * mn_group_elems, k_elem, ab0, ab1, ab2);
                         }
-                    } else if (!p.conv.pixels_along_k) {
-                        int s = int(tap % p.conv.taps_w), r = int(tap / p.conv.taps_w);
-                        if (p.conv.flip) { s = p.conv.taps_w - 1 - s; r = p.conv.taps_h - 1 - r; }
-                        tma_load_im2col_4d(a_dst, &p.tm_a, &full_bar[stage], int(k_in_tap), pw, ph, pn,
-                                           uint16_t(s * p.conv.dil_w), uint16_t(r * p.conv.dil_h));
+                    } else if (!pix_k) {
+                        const uint32_t s = p.conv.flip ? p.conv.taps_w - 1 - tap_s : tap_s;
+                        const uint32_t r = p.conv.flip ? p.conv.taps_h - 1 - tap_r : tap_r;
+                        tma_load_im2col_4d(a_dst, &p.tm_a, bar, int(k_in_tap), pw, ph, pn, uint16_t(s * p.conv.dil_w),
+                                           uint16_t(r * p.conv.dil_h));
                     } else {
-                        // dedw: rows of the tile are (tap, channel); k runs over pixels
-                        const uint32_t pix = k_elem;
-                        const uint32_t q = pix % p.conv.out_w;
-                        const uint32_t rest = pix / p.conv.out_w;
-                        const int w0 = int(q) * p.conv.stride_w + p.conv.lower_w;
-                        const int h0 = int(rest % p.conv.out_h) * p.conv.stride_h + p.conv.lower_h;
-                        const int n0i = int(rest / p.conv.out_h);
-                        for (uint32_t g = 0; g < a_groups; ++g) {
-                            const uint32_t m = tc.m0 + g * mn_group_elems;
-                            const uint32_t tp = m / p.conv.channels, c = m % p.conv.channels;
-                            const int s = int(tp % p.conv.taps_w), r = int(tp / p.conv.taps_w);
-                            tma_load_im2col_4d(a_dst + g * mn_group_bytes, &p.tm_a, &full_bar[stage], int(c), w0, h0, n0i,
-                                               uint16_t(s * p.conv.dil_w), uint16_t(r * p.conv.dil_h));
-                        }
+                        const int w0 = int(pq) * p.conv.stride_w + p.conv.lower_w;
+                        const int h0 = int(pp) * p.conv.stride_h + p.conv.lower_h;
+#pragma unroll
+                        for (uint32_t g = 0; g < 4; ++g)
+                            if (g < a_groups)
+                                tma_load_im2col_4d(a_dst + g * mn_group_bytes, &p.tm_a, bar, g_c[g], w0, h0, int(pimg), g_off_w[g], g_off_h[g]);
                     }
                     // ---- B
-                    {
-                        const int b0 = p.b_bcast[0] ? 0 : bi[0], b1 = p.b_bcast[1] ? 0 : bi[1], b2 = p.b_bcast[2] ? 0 : bi[2];
-                        if (!p.b_mn_major) {
-                            const uint32_t kc = p.conv.b_tap_local ? k_in_tap : k_elem;
-                            const uint32_t row = n0 + (p.conv.b_tap_local ? tap * p.conv.b_tap_rows : 0);
-                            tma_load_5d(b_dst, &p.tm_b, &full_bar[stage], kc, row, b0, b1, b2);
-                        } else {
-                            for (uint32_t g = 0; g < b_groups; ++g)
-                                tma_load_5d(b_dst + g * mn_group_bytes, &p.tm_b, &full_bar[stage], n0 + g * mn_group_elems,
-                                            k_elem, b0, b1, b2);
+                    if (!b_mn) {
+                        const uint32_t kc = p.conv.b_tap_local ? k_in_tap : k_elem;
+                        const uint32_t row = n0 + (p.conv.b_tap_local ? tap * p.conv.b_tap_rows : 0);
+                        tma_load_5d(b_dst, &p.tm_b, bar, kc, row, bb0, bb1, bb2);
+                    } else {
+#pragma unroll
+                        for (uint32_t g = 0; g < 8; ++g)
+                            if (g < b_groups)
+                                tma_load_5d(b_dst + g * mn_group_bytes, &p.tm_b, bar, n0 + g * mn_group_elems, k_elem, bb0, bb1, bb2);
+                    }
+                    // ---- advance
+                    k_elem += block_k;
+                    if (im2col && !pix_k) {
+                        k_in_tap += block_k;
+                        if (k_in_tap >= uint32_t(p.conv.k_blocks_per_tap) * block_k) {
+                            k_in_tap = 0;
+                            ++tap;
+                            if (++tap_s == uint32_t(p.conv.taps_w)) { tap_s = 0; ++tap_r; }
+                        }
+                    } else if (pix_k) {
+                        pq += block_k;
+                        while (pq >= uint32_t(p.conv.out_w)) {
+                            pq -= p.conv.out_w;
+                            if (++pp == uint32_t(p.conv.out_h)) { pp = 0; ++pimg; }
                         }
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -247,11 +327,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
+        // One thread issues all MMAs. The two shared-memory descriptors of a stage differ from
+        // stage 0's only in the start-address field, so each MMA costs two 64-bit adds.
         if (elect_one()) {
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             const uint32_t mn_k_step = (kUmmaKBytes / p.elem_bytes) * kRowBytes;  // MN-major: bytes per MMA along K
             const uint32_t mn_lbo = p.block_k * kRowBytes;
+            const uint32_t smem_base = smem_u32(smem);
+            const uint64_t a_desc0 = p.a_mn_major ? make_smem_desc(smem_base, mn_lbo, 1024) : make_smem_desc(smem_base, 16, 1024);
+            const uint64_t b_desc0 = p.b_mn_major ? make_smem_desc(smem_base + S::kABytes, mn_lbo, 1024)
+                                                  : make_smem_desc(smem_base + S::kABytes, 16, 1024);
+            const uint64_t a_step = (p.a_mn_major ? mn_k_step : uint32_t(kUmmaKBytes)) >> 4;
+            const uint64_t b_step = (p.b_mn_major ? mn_k_step : uint32_t(kUmmaKBytes)) >> 4;
+            constexpr uint64_t kStageUnits = S::kStageBytes >> 4;
+            const uint32_t idesc = p.idesc;
             for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const TileCoord tc = decode_tile(p, t);
                 if (!mbar_wait_bounded(&tmem_empty_bar[acc], acc_phase ^ 1, kWaitLimitNs)) {
@@ -260,6 +350,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
                 }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
+                uint32_t accumulate = 0;
                 for (uint32_t kb = tc.kb_begin; kb < tc.kb_end; ++kb) {
                     if (!mbar_wait_bounded(&full_bar[stage], phase, kWaitLimitNs)) {
                         atomicCAS(p.status, 0u, WAIT_MMA_FULL);
@@ -267,15 +358,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint32_t a_base = smem_u32(smem + stage * S::kStageBytes);
-                    const uint32_t b_base = a_base + S::kABytes;
+                    const uint64_t a_desc = a_desc0 + stage * kStageUnits;
+                    const uint64_t b_desc = b_desc0 + stage * kStageUnits;
 #pragma unroll
                     for (uint32_t k = 0; k < kRowBytes / kUmmaKBytes; ++k) {
-                        const uint64_t a_desc = p.a_mn_major ? make_smem_desc(a_base + k * mn_k_step, mn_lbo, 1024)
-                                                             : make_smem_desc(a_base + k * kUmmaKBytes, 16, 1024);
-                        const uint64_t b_desc = p.b_mn_major ? make_smem_desc(b_base + k * mn_k_step, mn_lbo, 1024)
-                                                             : make_smem_desc(b_base + k * kUmmaKBytes, 16, 1024);
-                        umma_ss<KIND>(d_tmem, a_desc, b_desc, p.idesc, (kb > tc.kb_begin || k > 0) ? 1u : 0u);
+                        umma_ss<KIND>(d_tmem, a_desc + k * a_step, b_desc + k * b_step, idesc, accumulate);
+                        accumulate = 1;
                     }
                     umma_commit(&empty_bar[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -290,99 +378,121 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
     } else if (warp >= 4) {
         // ------------------------------------------------------------------ epilogue
         const uint32_t sub = warp & 3;  // tensor-memory sub-partition this warp may read
+        const uint32_t epi_tid = threadIdx.x - 128;
         uint32_t acc = 0, acc_phase = 0;
         const uint32_t out_elem = dtype_size(int(p.out_dtype));
+        uint8_t* stage_out = smem + STAGES * S::kStageBytes + S::kBarrierBytes;  // 2 x [128 rows x 128 B], 1024-aligned
+        uint32_t store_buf = 0;
         for (uint32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
             const TileCoord tc = decode_tile(p, t);
             const uint32_t n0 = tc.n0 * BLOCK_N;
-            if (!mbar_wait_bounded(&tmem_full_bar[acc], acc_phase, kWaitLimitNs)) {
+            bool ready = mbar_wait_bounded(&tmem_full_bar[acc], acc_phase, kWaitLimitNs);
+            ready = __all_sync(0xffffffffu, ready);
+            if (!ready) {
                 atomicCAS(p.status, 0u, WAIT_EPILOGUE_TMEM_FULL);
                 break;
             }
             tc_fence_after_sync();
             const uint32_t row = tc.m0 + sub * 32 + lane;
-            uint64_t base_off;
-            if (p.split_k > 1) {
-                base_off = (uint64_t(tc.split) * p.batches + tc.batch) * uint64_t(p.M) * p.N + uint64_t(row) * p.N;
-            } else {
+            uint32_t bi[3];
+            {
                 uint32_t b = tc.batch;
-                const uint32_t i0 = b % p.bsz[0]; b /= p.bsz[0];
-                const uint32_t i1 = b % p.bsz[1]; b /= p.bsz[1];
-                base_off = i0 * p.out_bstride[0] + i1 * p.out_bstride[1] + b * p.out_bstride[2] + uint64_t(row) * p.out_ld;
+                bi[0] = b % p.bsz[0]; b /= p.bsz[0];
+                bi[1] = b % p.bsz[1]; b /= p.bsz[1];
+                bi[2] = b;
             }
             const uint64_t flat_row = (uint64_t(tc.batch) * p.M + row) * p.N;  // index base for the random stream
+            const uint32_t tmem_acc = tmem_base + acc * BLOCK_N + ((sub * 32) << 16);
+            if (p.tma_store) {
+                // ---- stage 128-byte-wide column chunks in shared memory (128-byte swizzle) and let the
+                //      copy engine write them: full-line, coalesced stores, edges clipped by the tensor map
+                const uint32_t cols_per_chunk = kRowBytes / out_elem;    // 32 fp32 / 64 bf16 / 128 fp8 columns
+                const uint32_t lds_per_chunk = cols_per_chunk / 32;
+                const uint32_t words_per_ld = 8 * out_elem;              // packed 32-bit words per 32 columns
 #pragma unroll 1
-            for (uint32_t ch = 0; ch < BLOCK_N / 32; ++ch) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(tmem_base + acc * BLOCK_N + ch * 32 + ((sub * 32) << 16), v);
-                tmem_ld_wait();
-                const uint32_t col0 = n0 + ch * 32;
-                if (row >= p.M || col0 >= p.N) continue;
-                const uint32_t ncols = min(32u, p.N - col0);
-                uint32_t elem = 4;
-                uint8_t* dst;
-                if (p.split_k > 1) {
-                    dst = reinterpret_cast<uint8_t*>(reinterpret_cast<float*>(p.out) + base_off + col0);
-                } else {
-                    elem = out_elem;
-                    dst = reinterpret_cast<uint8_t*>(p.out) + (base_off + col0) * out_elem;
-                    if (p.epi_mode == EPI_BF16_RNE) {
-                        // round-to-nearest-even with no flags: the hardware conversion gives the
-                        // reference's bits (NaN -> 0x7FFF, denormals kept)
+                for (uint32_t ch = 0; ch < BLOCK_N / cols_per_chunk; ++ch) {
+                    const uint32_t col0 = n0 + ch * cols_per_chunk;
+                    if (col0 >= p.N) break;  // uniform over the CTA
+                    uint8_t* buf = stage_out + store_buf * (kBlockM * kRowBytes);
+                    if (epi_tid == 0) tma_store_wait_read<1>();   // the store issued two chunks ago has drained this buffer
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    uint8_t* my_row = buf + (sub * 32 + lane) * kRowBytes;
+                    const uint32_t sw = (lane & 7);
+#pragma unroll 1
+                    for (uint32_t l = 0; l < lds_per_chunk; ++l) {
+                        uint32_t v[32];
+                        tmem_ld_32x32b_x32(tmem_acc + ch * cols_per_chunk + l * 32, v);
+                        tmem_ld_wait();
+                        epilogue_convert(v, p, out_elem, flat_row + col0 + l * 32);
+                        // words_per_ld packed words = words_per_ld / 4 sixteen-byte pieces of this row
+                        if (out_elem == 4) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const float lo = __uint_as_float(v[2 * j]) * p.scale, hi = __uint_as_float(v[2 * j + 1]) * p.scale;
-                            uint32_t packed;
-                            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
-                            v[j] = packed;
-                        }
-                    } else if (p.epi_mode == EPI_F32) {
+                            for (uint32_t q = 0; q < 8; ++q)
+                                *reinterpret_cast<uint4*>(my_row + (((l * 8 + q) ^ sw) << 4)) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                        } else if (out_elem == 2) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            uint32_t bits = __float_as_uint(__uint_as_float(v[j]) * p.scale);
-                            v[j] = f32_is_nan(bits) ? kF32CanonNan : bits;
-                        }
-                    } else {
+                            for (uint32_t q = 0; q < 4; ++q)
+                                *reinterpret_cast<uint4*>(my_row + (((l * 4 + q) ^ sw) << 4)) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            uint32_t bits = __float_as_uint(__uint_as_float(v[j]) * p.scale);
-                            if (f32_is_nan(bits)) bits = kF32CanonNan;
-                            if (p.cast.relu) bits = relu_bits(bits);
-                            uint32_t rnd = 0;
-                            if (p.rng_philox) rnd = philox_word(p.rng_seed, p.rng_offset, flat_row + col0 + j);
-                            v[j] = cast_from_f32(bits, p.cast, rnd);
-                        }
-                        // pack to the output width
-                        if (elem == 2) {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) v[j] = (v[2 * j] & 0xFFFFu) | (v[2 * j + 1] << 16);
-                        } else if (elem == 1) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                v[j] = (v[4 * j] & 0xFFu) | ((v[4 * j + 1] & 0xFFu) << 8) | ((v[4 * j + 2] & 0xFFu) << 16) | (v[4 * j + 3] << 24);
+                            for (uint32_t q = 0; q < 2; ++q)
+                                *reinterpret_cast<uint4*>(my_row + (((l * 2 + q) ^ sw) << 4)) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
                         }
                     }
+                    (void) words_per_ld;
+                    fence_proxy_async();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (epi_tid == 0) {
+                        tma_store_5d(&p.tm_out, buf, int(col0), int(tc.m0), int(bi[0]), int(bi[1]), int(bi[2]));
+                        tma_store_commit();
+                    }
+                    store_buf ^= 1;
                 }
-                // v[0 .. 8*elem) now holds 32 packed outputs
-                if (ncols == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-                    if (elem == 4) {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                    } else if (elem == 2) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 2; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                    }
+            } else {
+                uint64_t base_off;
+                if (p.split_k > 1) {
+                    base_off = (uint64_t(tc.split) * p.batches + tc.batch) * uint64_t(p.M) * p.N + uint64_t(row) * p.N;
                 } else {
-                    // ragged edge or unaligned row: element-wise, statically indexed
+                    base_off = bi[0] * p.out_bstride[0] + bi[1] * p.out_bstride[1] + bi[2] * p.out_bstride[2] + uint64_t(row) * p.out_ld;
+                }
+#pragma unroll 1
+                for (uint32_t ch = 0; ch < BLOCK_N / 32; ++ch) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(tmem_acc + ch * 32, v);
+                    tmem_ld_wait();
+                    const uint32_t col0 = n0 + ch * 32;
+                    if (row >= p.M || col0 >= p.N) continue;
+                    const uint32_t ncols = min(32u, p.N - col0);
+                    uint32_t elem = 4;
+                    uint8_t* dst;
+                    if (p.split_k > 1) {
+                        dst = reinterpret_cast<uint8_t*>(reinterpret_cast<float*>(p.out) + base_off + col0);
+                    } else {
+                        elem = out_elem;
+                        dst = reinterpret_cast<uint8_t*>(p.out) + (base_off + col0) * out_elem;
+                        epilogue_convert(v, p, out_elem, flat_row + col0);
+                    }
+                    // v[0 .. 8*elem) now holds 32 packed outputs
+                    if (ncols == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+                        if (elem == 4) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        if (uint32_t(j) < ncols) {
-                            if (elem == 4) reinterpret_cast<uint32_t*>(dst)[j] = v[j];
-                            else if (elem == 2) reinterpret_cast<uint16_t*>(dst)[j] = uint16_t(v[j / 2] >> (16 * (j & 1)));
-                            else dst[j] = uint8_t(v[j / 4] >> (8 * (j & 3)));
+                            for (int j = 0; j < 8; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        } else if (elem == 2) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 2; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        }
+                    } else {
+                        // ragged edge or unaligned row: element-wise, statically indexed
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (uint32_t(j) < ncols) {
+                                if (elem == 4) reinterpret_cast<uint32_t*>(dst)[j] = v[j];
+                                else if (elem == 2) reinterpret_cast<uint16_t*>(dst)[j] = uint16_t(v[j / 2] >> (16 * (j & 1)));
+                                else dst[j] = uint8_t(v[j / 4] >> (8 * (j & 3)));
+                            }
                         }
                     }
                 }
@@ -392,6 +502,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
         }
+        if (p.tma_store && epi_tid == 0) tma_store_wait_all<0>();  // shared memory must outlive the copies that read it
     }
 
     tc_fence_before_sync();
