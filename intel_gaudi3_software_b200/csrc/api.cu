@@ -360,7 +360,7 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
         TmaOperand od;
         od.ptr = o.ptr; od.elem = dtype_size(o.dtype); od.mn_major = false; od.inner = j.N; od.rows = j.M; od.row_stride = o.ld;
         for (int i = 0; i < 3; ++i) { od.bsz[i] = j.bsz[i]; od.bstride[i] = o.bstride[i]; }
-        if ((uint64_t(j.N) * od.elem) % 16 == 0 && tma_compatible(od) && encode_tiled(c, &p.tm_out, od, kRowBytes / od.elem, kBlockM, od.elem == 2 ? 2 : 0) == 0) p.tma_store = 1;
+        if ((uint64_t(j.N) * od.elem) % 16 == 0 && tma_compatible(od) && encode_tiled(c, &p.tm_out, od, kRowBytes / od.elem, 32, od.elem == 2 ? 2 : 0) == 0) p.tma_store = 1;
     }
 
     const unsigned grid = unsigned(std::min<uint64_t>(tiles * split, uint64_t(c->sm_count)));

@@ -6,8 +6,8 @@
 // (mme_reference_impl.cpp:661-689,1143-1245).
 //
 // CTA layout (256 threads):
-//   warp 0      TMA producer: fills a ring of STAGES operand tiles (A: 128 x 128 B, B: BLOCK_N x 128 B,
-//               both 128-byte swizzled) and signals full[stage] through complete_tx.
+//   warp 0, 3   TMA producers (A and B): fill a ring of STAGES operand tiles (A: 128 x 128 B,
+//               B: BLOCK_N x 128 B, both 128-byte swizzled) and signal full[stage] through complete_tx.
 //   warp 1      MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BLOCK_N, K=32 B) into one of
 //               two fp32 accumulators in tensor memory; tcgen05.commit frees the stage / publishes
 //               the accumulator.
@@ -60,7 +60,7 @@ struct ConvGeom {
 struct GemmParams {
     CUtensorMap tm_a;
     CUtensorMap tm_b;
-    CUtensorMap tm_out;      // output as (N, M, b0, b1, b2), box 128 B x 128 rows; used when tma_store != 0
+    CUtensorMap tm_out;      // output as (N, M, b0, b1, b2), box 128 B x 32 rows (one per epilogue warp); used when tma_store != 0
     uint32_t tma_store;
     uint32_t M, N, K;
     uint32_t block_k;       // elements per k block (128 B / element size)
@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&full_bar[s], 1);
+            mbar_init(&full_bar[s], 2);   // the A producer and the B producer each arrive once
             mbar_init(&empty_bar[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -200,23 +200,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
     const uint32_t tmem_base = *tmem_holder;
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer
-        // One thread feeds the ring. Everything that does not change inside a tile is computed
-        // before the k loop, and coordinates advance incrementally: no division per k block.
+        // ------------------------------------------------------------------ TMA producer for A
+        // One thread feeds A's half of the ring (warp 3 feeds B's). Everything that does not
+        // change inside a tile is computed before the k loop, and coordinates advance
+        // incrementally: no division per k block.
         if (elect_one()) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            const bool a_mn = p.a_mn_major != 0, b_mn = p.b_mn_major != 0;
+            const bool a_mn = p.a_mn_major != 0;
             const bool im2col = p.a_mode == A_IM2COL;
             const bool pix_k = im2col && p.conv.pixels_along_k;
             const uint32_t a_groups = a_mn ? (kBlockM * p.elem_bytes) / kRowBytes : 1;   // <= 4
-            const uint32_t b_groups = b_mn ? (BLOCK_N * p.elem_bytes) / kRowBytes : 1;   // <= 8
             const uint32_t mn_group_elems = kRowBytes / p.elem_bytes;
             const uint32_t mn_group_bytes = p.block_k * kRowBytes;
             const uint32_t block_k = p.block_k;
             for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const TileCoord tc = decode_tile(p, t);
-                const uint32_t n0 = tc.n0 * BLOCK_N;
                 uint32_t bi[3];
                 {
                     uint32_t b = tc.batch;
@@ -225,11 +224,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
                     bi[2] = b;
                 }
                 const int ab0 = p.a_bcast[0] ? 0 : bi[0], ab1 = p.a_bcast[1] ? 0 : bi[1], ab2 = p.a_bcast[2] ? 0 : bi[2];
-                const int bb0 = p.b_bcast[0] ? 0 : bi[0], bb1 = p.b_bcast[1] ? 0 : bi[1], bb2 = p.b_bcast[2] ? 0 : bi[2];
-                uint32_t k_elem = tc.kb_begin * block_k;   // K coordinate of plain (tiled) operands
+                uint32_t k_elem = tc.kb_begin * block_k;   // K coordinate of a plain (tiled) operand
                 // ---- per-tile im2col state
                 int pw = 0, ph = 0, pn = 0;                // base position of the tile's first pixel (fwd / dedx)
-                uint32_t tap_s = 0, tap_r = 0, k_in_tap = 0, tap = 0;   // fwd / dedx: filter tap and channel offset
+                uint32_t tap_s = 0, tap_r = 0, k_in_tap = 0;            // fwd / dedx: filter tap and channel offset
                 uint32_t pq = 0, pp = 0, pimg = 0;         // dedw: pixel position of the k block
                 uint16_t g_off_w[4] = {0, 0, 0, 0}, g_off_h[4] = {0, 0, 0, 0};
                 int g_c[4] = {0, 0, 0, 0};
@@ -239,7 +237,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
                     pw = int(q) * p.conv.stride_w + p.conv.lower_w;
                     ph = int(rest % p.conv.out_h) * p.conv.stride_h + p.conv.lower_h;
                     pn = int(rest / p.conv.out_h);
-                    tap = tc.kb_begin / p.conv.k_blocks_per_tap;
+                    const uint32_t tap = tc.kb_begin / p.conv.k_blocks_per_tap;
                     k_in_tap = (tc.kb_begin % p.conv.k_blocks_per_tap) * block_k;
                     tap_s = tap % p.conv.taps_w;
                     tap_r = tap / p.conv.taps_w;
@@ -267,10 +265,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
                         break;
                     }
                     uint8_t* a_dst = smem + stage * S::kStageBytes;
-                    uint8_t* b_dst = a_dst + S::kABytes;
                     uint64_t* bar = &full_bar[stage];
-                    mbar_arrive_expect_tx(bar, S::kStageBytes);
-                    // ---- A
+                    mbar_arrive_expect_tx(bar, S::kABytes);
                     if (!im2col) {
                         if (!a_mn) {
                             tma_load_5d(a_dst, &p.tm_a, bar, k_elem, tc.m0, ab0, ab1, ab2);
@@ -280,11 +276,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
                                 if (g < a_groups)
                                     tma_load_5d(a_dst + g * mn_group_bytes, &p.tm_a, bar, tc.m0 + g * mn_group_elems, k_elem, ab0, ab1, ab2);
                         }
+                        k_elem += block_k;
                     } else if (!pix_k) {
                         const uint32_t s = p.conv.flip ? p.conv.taps_w - 1 - tap_s : tap_s;
                         const uint32_t r = p.conv.flip ? p.conv.taps_h - 1 - tap_r : tap_r;
                         tma_load_im2col_4d(a_dst, &p.tm_a, bar, int(k_in_tap), pw, ph, pn, uint16_t(s * p.conv.dil_w),
                                            uint16_t(r * p.conv.dil_h));
+                        k_in_tap += block_k;
+                        if (k_in_tap >= uint32_t(p.conv.k_blocks_per_tap) * block_k) {
+                            k_in_tap = 0;
+                            if (++tap_s == uint32_t(p.conv.taps_w)) { tap_s = 0; ++tap_r; }
+                        }
                     } else {
                         const int w0 = int(pq) * p.conv.stride_w + p.conv.lower_w;
                         const int h0 = int(pp) * p.conv.stride_h + p.conv.lower_h;
@@ -292,34 +294,66 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
                         for (uint32_t g = 0; g < 4; ++g)
                             if (g < a_groups)
                                 tma_load_im2col_4d(a_dst + g * mn_group_bytes, &p.tm_a, bar, g_c[g], w0, h0, int(pimg), g_off_w[g], g_off_h[g]);
-                    }
-                    // ---- B
-                    if (!b_mn) {
-                        const uint32_t kc = p.conv.b_tap_local ? k_in_tap : k_elem;
-                        const uint32_t row = n0 + (p.conv.b_tap_local ? tap * p.conv.b_tap_rows : 0);
-                        tma_load_5d(b_dst, &p.tm_b, bar, kc, row, bb0, bb1, bb2);
-                    } else {
-#pragma unroll
-                        for (uint32_t g = 0; g < 8; ++g)
-                            if (g < b_groups)
-                                tma_load_5d(b_dst + g * mn_group_bytes, &p.tm_b, bar, n0 + g * mn_group_elems, k_elem, bb0, bb1, bb2);
-                    }
-                    // ---- advance
-                    k_elem += block_k;
-                    if (im2col && !pix_k) {
-                        k_in_tap += block_k;
-                        if (k_in_tap >= uint32_t(p.conv.k_blocks_per_tap) * block_k) {
-                            k_in_tap = 0;
-                            ++tap;
-                            if (++tap_s == uint32_t(p.conv.taps_w)) { tap_s = 0; ++tap_r; }
-                        }
-                    } else if (pix_k) {
                         pq += block_k;
                         while (pq >= uint32_t(p.conv.out_w)) {
                             pq -= p.conv.out_w;
                             if (++pp == uint32_t(p.conv.out_h)) { pp = 0; ++pimg; }
                         }
                     }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 3) {
+        // ------------------------------------------------------------------ TMA producer for B
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            const bool b_mn = p.b_mn_major != 0;
+            const bool tap_local = p.conv.b_tap_local != 0;
+            const uint32_t b_groups = b_mn ? (BLOCK_N * p.elem_bytes) / kRowBytes : 1;   // <= 8
+            const uint32_t mn_group_elems = kRowBytes / p.elem_bytes;
+            const uint32_t mn_group_bytes = p.block_k * kRowBytes;
+            const uint32_t block_k = p.block_k;
+            for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const TileCoord tc = decode_tile(p, t);
+                const uint32_t n0 = tc.n0 * BLOCK_N;
+                uint32_t bi[3];
+                {
+                    uint32_t b = tc.batch;
+                    bi[0] = b % p.bsz[0]; b /= p.bsz[0];
+                    bi[1] = b % p.bsz[1]; b /= p.bsz[1];
+                    bi[2] = b;
+                }
+                const int bb0 = p.b_bcast[0] ? 0 : bi[0], bb1 = p.b_bcast[1] ? 0 : bi[1], bb2 = p.b_bcast[2] ? 0 : bi[2];
+                uint32_t k_elem = tc.kb_begin * block_k;
+                uint32_t row = n0;
+                if (tap_local) {  // dedx: B's K coordinate restarts at every filter tap, its rows move on by C
+                    const uint32_t tap = tc.kb_begin / p.conv.k_blocks_per_tap;
+                    k_elem = (tc.kb_begin % p.conv.k_blocks_per_tap) * block_k;
+                    row = n0 + tap * p.conv.b_tap_rows;
+                }
+                const uint32_t k_wrap = tap_local ? uint32_t(p.conv.k_blocks_per_tap) * block_k : 0xFFFFFFFFu;
+                for (uint32_t kb = tc.kb_begin; kb < tc.kb_end; ++kb) {
+                    if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, kWaitLimitNs)) {
+                        atomicCAS(p.status, 0u, WAIT_PRODUCER_EMPTY);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* b_dst = smem + stage * S::kStageBytes + S::kABytes;
+                    uint64_t* bar = &full_bar[stage];
+                    mbar_arrive_expect_tx(bar, S::kBBytes);
+                    if (!b_mn) {
+                        tma_load_5d(b_dst, &p.tm_b, bar, k_elem, row, bb0, bb1, bb2);
+                    } else {
+#pragma unroll
+                        for (uint32_t g = 0; g < 8; ++g)
+                            if (g < b_groups)
+                                tma_load_5d(b_dst + g * mn_group_bytes, &p.tm_b, bar, n0 + g * mn_group_elems, k_elem, bb0, bb1, bb2);
+                    }
+                    k_elem += block_k;
+                    if (k_elem >= k_wrap) { k_elem = 0; row += p.conv.b_tap_rows; }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -378,7 +412,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
     } else if (warp >= 4) {
         // ------------------------------------------------------------------ epilogue
         const uint32_t sub = warp & 3;  // tensor-memory sub-partition this warp may read
-        const uint32_t epi_tid = threadIdx.x - 128;
         uint32_t acc = 0, acc_phase = 0;
         const uint32_t out_elem = dtype_size(int(p.out_dtype));
         uint8_t* stage_out = smem + STAGES * S::kStageBytes + S::kBarrierBytes;  // 2 x [128 rows x 128 B], 1024-aligned
@@ -408,23 +441,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
                 //      copy engine write them: full-line, coalesced stores, edges clipped by the tensor map
                 const uint32_t cols_per_chunk = kRowBytes / out_elem;    // 32 fp32 / 64 bf16 / 128 fp8 columns
                 const uint32_t lds_per_chunk = cols_per_chunk / 32;
-                const uint32_t words_per_ld = 8 * out_elem;              // packed 32-bit words per 32 columns
+                // each warp owns two 32-row x 128-byte buffers and issues its own stores: warps never
+                // wait for one another here
+                uint8_t* my_bufs = stage_out + sub * (2 * 32 * kRowBytes);
+                const uint32_t sw = (lane & 7);
 #pragma unroll 1
                 for (uint32_t ch = 0; ch < BLOCK_N / cols_per_chunk; ++ch) {
                     const uint32_t col0 = n0 + ch * cols_per_chunk;
                     if (col0 >= p.N) break;  // uniform over the CTA
-                    uint8_t* buf = stage_out + store_buf * (kBlockM * kRowBytes);
-                    if (epi_tid == 0) tma_store_wait_read<1>();   // the store issued two chunks ago has drained this buffer
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                    uint8_t* my_row = buf + (sub * 32 + lane) * kRowBytes;
-                    const uint32_t sw = (lane & 7);
+                    uint8_t* buf = my_bufs + store_buf * (32 * kRowBytes);
+                    if (lane == 0) tma_store_wait_read<1>();   // the store issued two chunks ago has drained this buffer
+                    __syncwarp();
+                    uint8_t* my_row = buf + lane * kRowBytes;
 #pragma unroll 1
                     for (uint32_t l = 0; l < lds_per_chunk; ++l) {
                         uint32_t v[32];
                         tmem_ld_32x32b_x32(tmem_acc + ch * cols_per_chunk + l * 32, v);
                         tmem_ld_wait();
                         epilogue_convert(v, p, out_elem, flat_row + col0 + l * 32);
-                        // words_per_ld packed words = words_per_ld / 4 sixteen-byte pieces of this row
                         if (out_elem == 4) {
 #pragma unroll
                             for (uint32_t q = 0; q < 8; ++q)
@@ -439,11 +473,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
                                 *reinterpret_cast<uint4*>(my_row + (((l * 2 + q) ^ sw) << 4)) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
                         }
                     }
-                    (void) words_per_ld;
                     fence_proxy_async();
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                    if (epi_tid == 0) {
-                        tma_store_5d(&p.tm_out, buf, int(col0), int(tc.m0), int(bi[0]), int(bi[1]), int(bi[2]));
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_5d(&p.tm_out, buf, int(col0), int(tc.m0 + sub * 32), int(bi[0]), int(bi[1]), int(bi[2]));
                         tma_store_commit();
                     }
                     store_buf ^= 1;
@@ -502,7 +535,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
         }
-        if (p.tma_store && epi_tid == 0) tma_store_wait_all<0>();  // shared memory must outlive the copies that read it
+        if (p.tma_store && lane == 0) tma_store_wait_all<0>();  // shared memory must outlive the copies that read it
     }
 
     tc_fence_before_sync();
