@@ -270,17 +270,37 @@ def run_ours(args):
             return (T(po, wl["out_dtype"], oshape, mem_space=space), T(px, abi.BF16, xs, mem_space=space),
                     T(pw, abi.BF16, ws, mem_space=space), T(py, abi.BF16, ys, mem_space=space))
         to, tx, tw, ty = tensors(dev[0].ptr, dev[1].ptr, dev[2].ptr, dout.ptr, abi.MEM_DEVICE)
-        reduce_buf = None
+        overlap = None
         if wl["op"] == abi.OP_DEDW and dist is not None:
+            # dW partials are all-reduced over NCCL on a second stream, double-buffered, so that the
+            # exchange of step i overlaps the convolution of step i+1 (as it would overlap the next
+            # layer's work in a training step)
             import torch
-            reduce_buf = torch.empty(int(np.prod(oshape)), dtype=torch.float32, device=torch.device("cuda", local))
-            to = T(reduce_buf.data_ptr(), abi.FP32, oshape, mem_space=abi.MEM_DEVICE)
-            calc.set_stream(torch.cuda.current_stream().cuda_stream)
+            dev_t = torch.device("cuda", local)
+            bufs = [torch.empty(int(np.prod(oshape)), dtype=torch.float32, device=dev_t) for _ in range(2)]
+            tos = [T(b.data_ptr(), abi.FP32, oshape, mem_space=abi.MEM_DEVICE) for b in bufs]
+            comm = torch.cuda.Stream(device=dev_t)
+            main = torch.cuda.current_stream(dev_t)
+            calc.set_stream(main.cuda_stream)
+            overlap = dict(i=0, done=[None, None])
 
         def step():
-            calc.do_convolution(to, tx, tw, ty, cp, wl["op"], abi.RM_NE, cast)
-            if reduce_buf is not None:
-                dist.all_reduce(reduce_buf)
+            if overlap is None:
+                calc.do_convolution(to, tx, tw, ty, cp, wl["op"], abi.RM_NE, cast)
+                return
+            k = overlap["i"] & 1
+            overlap["i"] += 1
+            if overlap["done"][k] is not None:
+                main.wait_event(overlap["done"][k])      # buffer k is free once its all-reduce finished
+            calc.do_convolution(tos[k], tx, tw, ty, cp, wl["op"], abi.RM_NE, cast)
+            ready = torch.cuda.Event()
+            ready.record(main)
+            with torch.cuda.stream(comm):
+                comm.wait_event(ready)
+                dist.all_reduce(bufs[k])
+                ev = torch.cuda.Event()
+                ev.record(comm)
+            overlap["done"][k] = ev
         used = {abi.OP_FWD: (0, 1), abi.OP_DEDX: (2, 1), abi.OP_DEDW: (0, 2)}[wl["op"]]
         in_bytes = sum(host[i].nbytes for i in used)
 
@@ -295,6 +315,10 @@ def run_ours(args):
     calc.timer_start()
     for _ in range(args.steps):
         step()
+    if wl["kind"] == "conv" and overlap is not None:
+        for ev in overlap["done"]:
+            if ev is not None:
+                main.wait_event(ev)                      # the timed region ends when the last exchange has
     ms = calc.timer_stop()
     calc.sync()
     clocks = sampler.stop() if sampler else None
@@ -327,7 +351,8 @@ def run_ours(args):
             calc.do_convolution(eo, ex, ew, ey, cp, wl["op"], abi.RM_NE, cast)
     if wl["kind"] == "conv":
         calc.set_stream(None)
-    e2e_step()
+    for _ in range(2):   # the first host-tensor calls size the library's staging arena
+        e2e_step()
     calc.sync()
     barrier_and_max(dist, 0.0, local)
     calc.timer_start()
@@ -338,6 +363,9 @@ def run_ours(args):
     e2e_value = world * flops / (e2e_ms * 1e-3) / 1e12
     result_checksum = int(np.frombuffer((C.c_uint8 * min(out_bytes, 4096)).from_address(hout), dtype=np.uint8).sum())
 
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
     if rank != 0:
         return
     peaks = measured_peaks()

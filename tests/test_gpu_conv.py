@@ -136,13 +136,33 @@ def test_fused_bf16_output(calc, best_oracle, port):
     assert inexact < 0.02 * n
 
 
+def test_transposed_dedx(calc, golden):
+    """transposed_dedx == dedx on weights with their two fastest dims swapped and S mirrored; checked
+    against the reference's own output (golden) and against dedx on host-flipped weights (bit-identical)."""
+    c = CONV_CASES[0]
+    xs, ws, ys = conv_shapes(c)
+    cp = abi.make_conv_params(2, c[8], c[7], c[9])
+    wt_shape = [ws[1], ws[0], ws[2], ws[3]]
+    wt = golden["tdedx_w"]
+    x, y = T(golden["conv0_x"], abi.BF16, xs), T(golden["conv0_y"], abi.BF16, ys)
+    o = np.zeros(int(np.prod(xs)), np.float32)
+    calc.do_convolution(T(o, abi.FP32, xs), x, T(wt, abi.BF16, wt_shape), y, cp, abi.OP_TRANSPOSED_DEDX)
+    g = golden["tdedx_out"]
+    assert np.abs(o - g).max() <= 2e-5 * np.abs(g).max()
+    w4 = wt.reshape(wt_shape[3], wt_shape[2], wt_shape[1], wt_shape[0])          # (R, S, i1, i0)
+    flipped = np.ascontiguousarray(w4[:, ::-1].transpose(0, 1, 3, 2))               # (R, S', i0, i1) -> [K, C, S, R] memory
+    o2 = np.zeros(int(np.prod(xs)), np.float32)
+    calc.do_convolution(T(o2, abi.FP32, xs), x, T(flipped, abi.BF16, ws), y, cp, abi.OP_DEDX)
+    assert (o.view(np.uint32) == o2.view(np.uint32)).all()
+
+
 def test_errors(calc):
     a = np.zeros(4096, np.uint16)
     cp = abi.make_conv_params(2)
     with pytest.raises(pkg.MmeError):  # output shape is not y's shape
         calc.do_convolution(T(np.zeros(10, np.float32), abi.FP32, [2, 5, 1, 1]), T(a, abi.BF16, [4, 4, 4, 1]), T(a, abi.BF16, [2, 4, 1, 1]),
                             T(a, abi.BF16, [2, 4, 4, 1]), cp, abi.OP_FWD)
-    with pytest.raises(pkg.MmeError) as ei:
-        calc.do_convolution(T(np.zeros(32, np.float32), abi.FP32, [2, 4, 4, 1]), T(a, abi.BF16, [4, 4, 4, 1]), T(a, abi.BF16, [2, 4, 1, 1]),
-                            T(a, abi.BF16, [2, 4, 4, 1]), cp, abi.OP_TRANSPOSED_DEDX)
+    with pytest.raises(pkg.MmeError) as ei:   # integer activations: outside this backend, never a CPU result
+        calc.do_convolution(T(np.zeros(32, np.float32), abi.FP32, [2, 4, 4, 1]), T(a, 2, [4, 4, 4, 1]), T(a, 2, [2, 4, 1, 1]),
+                            T(a, 2, [2, 4, 4, 1]), cp, abi.OP_FWD)
     assert ei.value.status == abi.ERR_UNSUPPORTED

@@ -226,3 +226,22 @@ def test_device_resident_tensors(calc, best_oracle):
     assert np.abs(o - r).max() <= util.ACC_TOL * K / 4
     for b in (dx, dw, do):
         b.free()
+
+
+def test_large_host_tensor_gemm_runs_pipelined_and_matches_device_path(calc):
+    """Host-tensor GEMMs above 32 MiB upload / multiply / download in row blocks on three streams; every
+    output row must be bit-identical to the single-launch device path (same reduction per row)."""
+    rng = np.random.default_rng(33)
+    M, N, K = 4352, 2048, 2048   # 17 tiles of rows: the last row block is ragged
+    xb, wb = util.gen_bf16(rng, M * K), util.gen_bf16(rng, K * N)
+    for op, ws in ((abi.OP_AB, [N, K]), (abi.OP_ABT, [K, N])):
+        host = np.zeros(M * N, np.uint16)
+        cp = abi.make_cast_params(abi.RM_SR, clip_fp=True, rng_kind=abi.RNG_PHILOX, rng_seed=3, rng_offset=17)
+        calc.do_batch_gemm(T(host, abi.BF16, [N, M]), T(xb, abi.BF16, [K, M]), T(wb, abi.BF16, ws), op, cp)
+        dx, dw, do = calc.to_device(xb), calc.to_device(wb), calc.alloc(M * N * 2)
+        calc.do_batch_gemm(T(do.ptr, abi.BF16, [N, M], mem_space=1), T(dx.ptr, abi.BF16, [K, M], mem_space=1),
+                           T(dw.ptr, abi.BF16, ws, mem_space=1), op, cp)
+        calc.sync(10_000_000_000)
+        assert (host == do.download(np.uint16)).all(), op
+        for b in (dx, dw, do):
+            b.free()
