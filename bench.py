@@ -406,6 +406,9 @@ def run_ours(args):
     print(json.dumps(line))
 
 
+_CPU_W_CACHE = {}
+
+
 def cpu_sample(wl, rows_hint=None):
     """Bounded sample of the workload for the CPU calculator: a block of A's rows against all of B
     (whole common dimension), or a few output rows of the convolution's GEMM."""
@@ -418,9 +421,17 @@ def cpu_sample(wl, rows_hint=None):
 def cpu_run(lib, wl, rows, threads, seed=1000):
     """One bounded CPU sample; returns (seconds, flops)."""
     if wl["kind"] == "gemm":
-        x, w = synth_inputs(dict(wl, batch=1), seed, rows=rows)
+        import util
         N, K = wl["N"], wl["K"]
-        w = w[:K * N]
+        key = (wl["w_dtype"], N, K, seed)
+        if key not in _CPU_W_CACHE:   # B is the same for every sample of a run: draw it once
+            r = np.random.default_rng(seed + 1)
+            _CPU_W_CACHE[key] = (util.f32_to_bf16_rne(r.uniform(-1, 1, K * N).astype(np.float32)) if wl["w_dtype"] == abi.BF16
+                                 else quantise_fp8(r.standard_normal(K * N, dtype=np.float32), wl["w_dtype"], 7))
+        w = _CPU_W_CACHE[key]
+        r = np.random.default_rng(seed)
+        x = (util.f32_to_bf16_rne(r.uniform(-1, 1, rows * K).astype(np.float32)) if wl["in_dtype"] == abi.BF16
+             else quantise_fp8(r.standard_normal(rows * K, dtype=np.float32), wl["in_dtype"], 7))
         x_bias = wl["bias"] if wl["in_dtype"] == abi.FP8_143 else 15
         w_bias = 7 if wl["in_dtype"] != abi.FP8_143 else wl["bias"]
         mode = lambda dt: abi.INFNAN_MINIMAL if dt == abi.FP8_143 else abi.INFNAN_FULL  # noqa: E731
@@ -498,7 +509,8 @@ def run_reference(args):
         "impl": "reference", "metric": "GEMM/conv TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": t / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
-        "config": {"workload": args.workload, "note": "CPU calculator on host cores; each step is a bounded sample"},
+        "config": {"workload": args.workload, "per_gpu": {k: v for k, v in wl.items() if k in ("M", "N", "K", "batch")} or CONV,
+                   "accumulate": "fp32", "note": "reference CPU calculator on the host cores; each step is a bounded sample: " + sample},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": lib.kind, "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,

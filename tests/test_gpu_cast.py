@@ -123,12 +123,15 @@ def test_memory_write(calc, port):
     base[:3] = [1e-40, -1e-40, 3e38]
     src = rng.normal(0, 1, n).astype(np.float32)
     src[2] = 3e38
-    for rm in (0, 1, 2, 3):
-        for clip in (0, 1):
-            m1, m2 = base.copy(), base.copy()
-            assert port.memory_write(T(m1, abi.FP32, [n]), T(src, abi.FP32, [n]), abi.RED_ADD, rm, clip) == 0
-            calc.do_memory_write(T(m2, abi.FP32, [n]), T(src, abi.FP32, [n]), abi.RED_ADD, rm, clip)
-            assert (m1.view(np.uint32) == m2.view(np.uint32)).all(), (rm, clip)
+    base[5:9] = [np.nan, 0.0, -0.0, -1.0]
+    src[5:9] = [1.0, -0.0, 0.0, np.nan]
+    for op in (abi.RED_ADD, abi.RED_SUB, abi.RED_MIN, abi.RED_MAX, abi.RED_MAX_0):
+        for rm in (0, 1, 2, 3):
+            for clip in (0, 1):
+                m1, m2 = base.copy(), base.copy()
+                assert port.memory_write(T(m1, abi.FP32, [n]), T(src, abi.FP32, [n]), op, rm, clip) == 0
+                calc.do_memory_write(T(m2, abi.FP32, [n]), T(src, abi.FP32, [n]), op, rm, clip)
+                assert (m1.view(np.uint32) == m2.view(np.uint32)).all(), (op, rm, clip)
     m = base.copy()
     calc.do_memory_write(T(m, abi.FP32, [n]), T(src, abi.FP32, [n]))  # reduction none = copy
     assert (m.view(np.uint32) == src.view(np.uint32)).all()

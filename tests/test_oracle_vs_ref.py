@@ -96,15 +96,21 @@ def test_conv_3d(port, ref):
         assert same(o1, o2), op
 
 
-def test_memory_write_add(port, ref):
+def test_memory_write_reductions(port, ref):
     rng = np.random.default_rng(7)
     m1 = rng.normal(0, 1, 300).astype(np.float32)
     m1[:3] = [1e-40, -1e-40, 3e38]
     m2 = m1.copy()
     s = rng.normal(0, 1, 300).astype(np.float32)
     s[2] = 3e38
-    for rm in (0, 1, 2, 3):
-        for clip in (0, 1):
-            assert port.memory_write(T(m1, abi.FP32, [300]), T(s, abi.FP32, [300]), abi.RED_ADD, rm, clip) == 0
-            assert ref.memory_write(T(m2, abi.FP32, [300]), T(s, abi.FP32, [300]), abi.RED_ADD, rm, clip) == 0
-            assert same(m1, m2), (rm, clip)
+    m1[5:9] = [np.nan, 0.0, -0.0, -1.0]
+    s[5:9] = [1.0, -0.0, 0.0, np.nan]
+    m2 = m1.copy()
+    base = m1.copy()
+    for op in (abi.RED_ADD, abi.RED_SUB, abi.RED_MIN, abi.RED_MAX, abi.RED_MAX_0):
+        for rm in (0, 1, 2, 3):
+            for clip in (0, 1):
+                m1[:], m2[:] = base, base
+                assert port.memory_write(T(m1, abi.FP32, [300]), T(s, abi.FP32, [300]), op, rm, clip) == 0
+                assert ref.memory_write(T(m2, abi.FP32, [300]), T(s, abi.FP32, [300]), op, rm, clip) == 0
+                assert same(m1, m2), (op, rm, clip)
