@@ -53,6 +53,9 @@ WORKLOADS = {
     "conv_fwd": dict(kind="conv", op=abi.OP_FWD, out_dtype=abi.BF16, bound="tensor", peak_scale=1.0, dtype="bf16"),
     "conv_dedx": dict(kind="conv", op=abi.OP_DEDX, out_dtype=abi.BF16, bound="tensor", peak_scale=1.0, dtype="bf16"),
     "conv_dedw": dict(kind="conv", op=abi.OP_DEDW, out_dtype=abi.FP32, bound="tensor", peak_scale=1.0, dtype="bf16"),
+    # same convolution, the cross-GPU sum fused into the split-K reduction (peer stores + rank-ordered gather)
+    "conv_dedw_fused": dict(kind="conv", op=abi.OP_DEDW, out_dtype=abi.FP32, bound="tensor", peak_scale=1.0, dtype="bf16",
+                            fused_exchange=True),
 }
 CONV = dict(C=256, K=256, W=56, H=56, B=64, S=3, R=3, pad=1)
 
@@ -271,7 +274,11 @@ def run_ours(args):
                     T(pw, abi.BF16, ws, mem_space=space), T(py, abi.BF16, ys, mem_space=space))
         to, tx, tw, ty = tensors(dev[0].ptr, dev[1].ptr, dev[2].ptr, dout.ptr, abi.MEM_DEVICE)
         overlap = None
-        if wl["op"] == abi.OP_DEDW and dist is not None:
+        exchange = None
+        if wl.get("fused_exchange"):
+            from intel_gaudi3_software_b200.multi_gpu import PeerExchange
+            exchange = PeerExchange(calc, int(np.prod(oshape)), dist, rank, world)
+        elif wl["op"] == abi.OP_DEDW and dist is not None:
             # dW partials are all-reduced over NCCL on a second stream, double-buffered, so that the
             # exchange of step i overlaps the convolution of step i+1 (as it would overlap the next
             # layer's work in a training step)
@@ -285,6 +292,9 @@ def run_ours(args):
             overlap = dict(i=0, done=[None, None])
 
         def step():
+            if exchange is not None:
+                exchange.dedw_allreduce(to, tx, tw, ty, cp)
+                return
             if overlap is None:
                 calc.do_convolution(to, tx, tw, ty, cp, wl["op"], abi.RM_NE, cast)
                 return
@@ -392,7 +402,8 @@ def run_ours(args):
                    "l2": "operands + output (%d MiB) exceed the 126 MB L2; no flush between steps" % ((in_bytes + out_bytes) >> 20)
                    if in_bytes + out_bytes > L2_BYTES else "working set fits L2 (latency-bound correctness config)",
                    "sharding": "rows of A / images per rank, replica of B / weights" if wl.get("op") != abi.OP_DEDW else
-                   "reduction dim sharded; fp32 partials all-reduced over NCCL"},
+                   ("reduction dim sharded; fp32 partials exchanged by the reduction kernel itself over peer memory"
+                    if wl.get("fused_exchange") else "reduction dim sharded; fp32 partials all-reduced over NCCL (overlapped)")},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes,
                 "ms_per_step": e2e_ms, "result_checksum": result_checksum},
         "gpu_launches": launches,

@@ -54,6 +54,17 @@ class CastParams(C.Structure):
                 ("reserved", C.c_int32), ("rng_seed", C.c_uint64), ("rng_offset", C.c_uint64)]
 
 
+class PeerGroup(C.Structure):
+    """mmeb200_peer_group: slot buffers and arrival flags of the ranks taking part in a fused dedw exchange."""
+    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("slots", C.c_void_p * 8), ("flags", C.c_void_p * 8),
+                ("step", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+class CompareResult(C.Structure):
+    """mmeb200_compare_result."""
+    _fields_ = [("mismatches", C.c_uint64), ("first_index", C.c_uint64)]
+
+
 def dense_strides(sizes):
     s, acc = [], 1
     for n in sizes:
@@ -145,6 +156,11 @@ SYMBOLS = {
     "mmeb200_timer_stop": (C.c_int, [C.c_void_p, P(C.c_float)]),
     "mmeb200_launch_count": (C.c_uint64, [C.c_void_p]),
     "mmeb200_version": (C.c_char_p, []),
+    "mmeb200_compare": (C.c_int, [C.c_void_p, P(Tensor), P(Tensor), C.c_uint, C.c_uint, C.c_int, P(CompareResult)]),
+    "mmeb200_peer_alloc": (C.c_int, [C.c_void_p, C.c_size_t, P(C.c_void_p), C.c_char_p]),
+    "mmeb200_peer_open": (C.c_int, [C.c_void_p, C.c_char_p, P(C.c_void_p)]),
+    "mmeb200_peer_close": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "mmeb200_conv_dedw_allreduce": (C.c_int, [C.c_void_p, P(Tensor), P(Tensor), P(Tensor), P(Tensor), P(ConvParams), P(PeerGroup)]),
     "mmeb200_gemm_splitk_static": (C.c_int, [C.c_void_p, P(Tensor), P(Tensor), P(Tensor), C.c_int, C.c_int]),
 }
 

@@ -101,6 +101,30 @@ class Calculator:
     def convert(self, out, inp, cast=None):
         self._check(self.lib.mmeb200_convert(self.ctx, out, inp, cast))
 
+    def compare(self, a, b, cd_size, num_partials=1, bit_exact=False):
+        """TensorComparator::doCompare / doCompareBitExact on the device: (mismatching elements, lowest mismatching index)."""
+        r = abi.CompareResult()
+        self._check(self.lib.mmeb200_compare(self.ctx, a, b, cd_size, num_partials, int(bit_exact), C.byref(r)))
+        return int(r.mismatches), int(r.first_index)
+
+    def peer_alloc(self, nbytes):
+        """Zero-filled device memory that other processes can map: returns (device pointer, 64-byte handle)."""
+        ptr = C.c_void_p()
+        handle = C.create_string_buffer(64)
+        self._check(self.lib.mmeb200_peer_alloc(self.ctx, nbytes, C.byref(ptr), handle))
+        return ptr.value, handle.raw
+
+    def peer_open(self, handle):
+        ptr = C.c_void_p()
+        self._check(self.lib.mmeb200_peer_open(self.ctx, handle, C.byref(ptr)))
+        return ptr.value
+
+    def peer_close(self, ptr):
+        self._check(self.lib.mmeb200_peer_close(self.ctx, ptr))
+
+    def do_convolution_dedw_allreduce(self, out, x, w, y, params, group):
+        self._check(self.lib.mmeb200_conv_dedw_allreduce(self.ctx, out, x, w, y, params, group))
+
     def gemm_splitk_static(self, out, x, w, op, splits):
         """Split-K GEMM whose partial sums live in the library's fixed 16 MiB device array: for callers
         that may not allocate (see include/mme_b200.h). Device tensors only."""

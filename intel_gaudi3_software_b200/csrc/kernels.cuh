@@ -293,6 +293,104 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, ReduceOut r) 
 }
 
 // ---------------------------------------------------------------------------------------------
+// dedw across GPUs, fused with the split-K reduction: every rank sums its K-splits (ascending)
+// and stores the result straight into slot [rank] of EVERY rank's slot buffer over NVLink (plain
+// peer stores; no TMA, no multicast), then bumps an arrival counter on every rank. A second kernel
+// waits (bounded) until all ranks have arrived and adds the slots in rank order, so all ranks hold
+// bit-identical sums. This is the multi-GPU form of summing dedw partials with doMemoryWrite's
+// fp32 add (mme/mme_reference/mme_reference_impl.cpp:718-768).
+// ---------------------------------------------------------------------------------------------
+constexpr int kMaxPeers = 8;
+struct PeerScatter {
+    float* slots[kMaxPeers];      // slots[j] = base of rank j's slot buffer: world x n floats
+    uint32_t* flags[kMaxPeers];   // flags[j] = arrival counter living on rank j
+    uint32_t* block_counter;      // local: counts finished blocks of this launch (reset by the last one)
+    uint32_t rank, world, splits;
+    uint64_t n;                   // floats per slot (M * N)
+    float scale;
+};
+
+__global__ void splitk_reduce_peer_scatter_kernel(const float* __restrict__ ws, PeerScatter p) {
+    const uint64_t n4 = p.n / 4;  // the host guarantees n % 4 == 0
+    const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t k = 0; k < p.splits; ++k) {
+            const float4 v = reinterpret_cast<const float4*>(ws + uint64_t(k) * p.n)[i];
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        s.x *= p.scale; s.y *= p.scale; s.z *= p.scale; s.w *= p.scale;
+        // start with the next rank so that the eight senders do not all hit the same receiver at once
+        for (uint32_t d = 0; d < p.world; ++d) {
+            const uint32_t j = (p.rank + 1 + d) % p.world;
+            reinterpret_cast<float4*>(p.slots[j] + uint64_t(p.rank) * p.n)[i] = s;
+        }
+    }
+    // publish: every thread's peer stores are ordered before the block's arrival; the last block of
+    // the launch then tells every rank that this rank's slot is complete
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t done = atomicAdd(p.block_counter, 1u) + 1;
+        if (done == gridDim.x) {
+            *p.block_counter = 0;
+            __threadfence_system();
+            for (uint32_t j = 0; j < p.world; ++j) atomicAdd_system(p.flags[j], 1u);
+        }
+    }
+}
+
+struct PeerGather {
+    const float* my_slots;        // this rank's slot buffer: world x n floats
+    const uint32_t* my_flag;      // this rank's arrival counter
+    uint32_t target;              // value the counter reaches when every rank has delivered this exchange
+    uint32_t world;
+    uint64_t n;
+    float* out;
+    uint32_t* status;
+    uint64_t limit_ns;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void peer_gather_sum_kernel(PeerGather p) {
+    __shared__ int ok;
+    if (threadIdx.x == 0) {
+        // wrap-safe compare; the wait is bounded: on expiry the kernel reports and leaves
+        uint64_t t0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        int good = 1;
+        uint32_t spins = 0;
+        while (int32_t(ld_acquire_sys(p.my_flag) - p.target) < 0) {
+            if ((++spins & 0xff) == 0) {
+                uint64_t t;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+                if (t - t0 > p.limit_ns) { good = 0; break; }
+            }
+        }
+        if (!good) atomicCAS(p.status, 0u, 16u);
+        ok = good;
+    }
+    __syncthreads();
+    if (!ok) return;
+    const uint64_t n4 = p.n / 4;
+    const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t r = 0; r < p.world; ++r) {
+            // slots were written by other GPUs: read them past L1
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(p.my_slots + uint64_t(r) * p.n) + i);
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        reinterpret_cast<float4*>(p.out)[i] = s;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // doMemoryWrite reductions on fp32 (mme_reference_impl.cpp:718-768 over the RMW add of
 // coral-sim/src/gaudi3/fs_core/fs_fma.cpp:2396-2408 and the subtract twin): mem = mem (+|-) src
 // in the given direction, denormal inputs and results flushed, optional clip of a fresh Inf.
@@ -353,6 +451,47 @@ __global__ void strided_copy_kernel(void* __restrict__ out, const void* __restri
         if (p.elem == 1) reinterpret_cast<uint8_t*>(out)[dof] = reinterpret_cast<const uint8_t*>(in)[so];
         else if (p.elem == 2) reinterpret_cast<uint16_t*>(out)[dof] = reinterpret_cast<const uint16_t*>(in)[so];
         else reinterpret_cast<uint32_t*>(out)[dof] = reinterpret_cast<const uint32_t*>(in)[so];
+    }
+}
+
+// TensorComparator::doCompare on the device: `a` holds num_partials stacked results (summed in fp32,
+// in order, then rounded to the element type) and `b` the tensor to compare with; counts mismatching
+// elements and finds the lowest mismatching index. bit_exact compares raw bits instead.
+struct CompareParams {
+    const void* a;
+    const void* b;
+    uint64_t n;              // elements of b
+    uint32_t num_partials;
+    int elem, bit_exact;
+    CompareSpec spec;
+    unsigned long long* mismatches;   // [0] count, [1] lowest index (initialised to ~0)
+};
+__device__ __forceinline__ uint32_t load_raw(const void* p, uint64_t i, int elem) {
+    if (elem == 1) return reinterpret_cast<const uint8_t*>(p)[i];
+    if (elem == 2) return reinterpret_cast<const uint16_t*>(p)[i];
+    return reinterpret_cast<const uint32_t*>(p)[i];
+}
+__global__ void compare_kernel(CompareParams p) {
+    const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
+    unsigned long long bad = 0, first = ~0ull;
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < p.n; i += stride) {
+        uint32_t a_raw;
+        if (p.num_partials == 1) {
+            a_raw = load_raw(p.a, i, p.elem);
+        } else {
+            float sum = 0.0f;
+            for (uint32_t k = 0; k < p.num_partials; ++k)
+                sum += __uint_as_float(decode_to_f32(load_raw(p.a, uint64_t(k) * p.n + i, p.elem), p.spec.dtype, p.spec.bias, p.spec.mode));
+            a_raw = (p.spec.dtype == DT_BF16) ? f32_to_bf16(__float_as_uint(sum), RM_NE, 0, false, false, false)
+                                              : f32_to_f32(__float_as_uint(sum), RM_NE, false, false);
+        }
+        const uint32_t b_raw = load_raw(p.b, i, p.elem);
+        const bool same = p.bit_exact ? (a_raw == b_raw) : compare_elements(a_raw, b_raw, p.spec);
+        if (!same) { ++bad; if (i < first) first = i; }
+    }
+    if (bad) {
+        atomicAdd(p.mismatches, bad);
+        atomicMin(p.mismatches + 1, first);
     }
 }
 

@@ -77,3 +77,54 @@ class ShardedCalculator:
         if self.world > 1:
             all_reduce_sum()
         return b, e
+
+
+class PeerExchange:
+    """Slot buffers and flags for the fused dedw exchange (mmeb200_conv_dedw_allreduce), double-buffered.
+
+    Every rank allocates two slot buffers (world x n fp32) and two flags, publishes their handles with
+    `all_gather_object` (any torch.distributed backend; world == 1 needs none) and opens the peers'.
+    `dedw_allreduce` alternates between the two sets, which is what lets ranks drift apart by one step.
+    """
+
+    def __init__(self, calc, n_floats, dist=None, rank=0, world=1):
+        assert 1 <= world <= 8
+        self.calc, self.rank, self.world, self.n = calc, rank, world, n_floats
+        self.calls = 0
+        mine = []
+        for _ in range(2):
+            slots, hs = calc.peer_alloc(world * n_floats * 4)
+            flag, hf = calc.peer_alloc(256)
+            mine.append((slots, hs, flag, hf))
+        handles = [[(m[1], m[3]) for m in mine]]
+        if world > 1:
+            gathered = [None] * world
+            dist.all_gather_object(gathered, handles[0])
+            handles = gathered
+        self.opened = []
+        self.groups = []
+        for b in range(2):
+            g = abi.PeerGroup()
+            g.rank, g.world, g.step = rank, world, 0
+            for j in range(world):
+                if j == rank:
+                    g.slots[j], g.flags[j] = mine[b][0], mine[b][2]
+                else:
+                    sp, fp = calc.peer_open(handles[j][b][0]), calc.peer_open(handles[j][b][1])
+                    self.opened += [sp, fp]
+                    g.slots[j], g.flags[j] = sp, fp
+            self.groups.append(g)
+        if world > 1:
+            dist.barrier()   # nobody starts before every rank has mapped every buffer
+
+    def dedw_allreduce(self, out, x, w, y, params):
+        """dW over this rank's images, summed over all ranks into `out` (fp32), asynchronously on the calculator's stream."""
+        g = self.groups[self.calls & 1]
+        g.step = self.calls >> 1
+        self.calc.do_convolution_dedw_allreduce(out, x, w, y, params, g)
+        self.calls += 1
+
+    def close(self):
+        for ptr in self.opened:
+            self.calc.peer_close(ptr)
+        self.opened = []

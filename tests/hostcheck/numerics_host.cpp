@@ -25,6 +25,16 @@ void hc_cast(const uint32_t* in, uint8_t* out, size_t n, int out_dtype, int exp_
         for (int k = 0; k < es; k++) out[i * es + k] = uint8_t(v >> (8 * k));
     }
 }
+void hc_compare(const uint8_t* a, const uint8_t* b, uint8_t* equal, size_t n, int dtype, int bias, int mode, unsigned cd)
+{
+    const CompareSpec c = make_compare_spec(dtype, bias, mode, cd);
+    const int es = dtype_size(dtype);
+    for (size_t i = 0; i < n; i++) {
+        uint32_t ra = 0, rb = 0;
+        for (int k = 0; k < es; k++) { ra |= uint32_t(a[i * es + k]) << (8 * k); rb |= uint32_t(b[i * es + k]) << (8 * k); }
+        equal[i] = compare_elements(ra, rb, c) ? 1 : 0;
+    }
+}
 int hc_fp8_foreign(uint32_t code, int exp_width, int mode) { return fp8_code_is_foreign(code, exp_width, mode); }
 uint32_t hc_lfsr(uint32_t v, uint32_t poly) { return lfsr32_step(v, poly); }
 uint32_t hc_philox(uint64_t seed, uint64_t offset, uint64_t index) { return philox_word(seed, offset, index); }

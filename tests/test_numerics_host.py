@@ -106,3 +106,45 @@ def test_philox_word_never_zero_and_uniform(hc):
     for bit in (31, 13):
         ones = int(((w >> bit) & 1).sum())
         assert abs(ones - 10000) < 5 * 71
+
+
+def comparator_pairs(dtype, rng, n=6000):
+    """Pairs that land on every branch of the rule: identical, a few ulps apart, far apart, sign flips, zeros, Inf / NaN."""
+    if dtype == abi.FP32:
+        a = (rng.normal(0, 1, n) * 10.0 ** rng.integers(-3, 4, n)).astype(np.float32)
+        b = a.copy()
+        k = n // 6
+        b[:k] = (a[:k].view(np.uint32) + rng.integers(0, 12, k).astype(np.uint32)).view(np.float32)
+        b[k:2 * k] = a[k:2 * k] * rng.uniform(0.8, 1.2, k).astype(np.float32)
+        b[2 * k:3 * k] = -a[2 * k:3 * k]
+        b[3 * k:3 * k + 8] = [0, -0.0, np.inf, -np.inf, np.nan, 1e-3, 0.04, 0.06]
+        a[3 * k + 4:3 * k + 8] = [1.0, 0.0, 0.0, 0.0]
+        return a.view(np.uint32), b.view(np.uint32)
+    if dtype == abi.BF16:
+        a = rng.integers(0, 65536, n).astype(np.uint16)
+        b = a.copy()
+        k = n // 4
+        b[:k] = (a[:k].astype(np.int32) + rng.integers(-9, 10, k)).astype(np.uint16)
+        b[k:2 * k] = rng.integers(0, 65536, k).astype(np.uint16)
+        b[2 * k:3 * k] = a[2 * k:3 * k] ^ 0x8000
+        return a, b
+    a = rng.integers(0, 256, n).astype(np.uint8)
+    b = a.copy()
+    k = n // 4
+    b[:k] = (a[:k].astype(np.int32) + rng.integers(-6, 7, k)).astype(np.uint8)
+    b[k:2 * k] = rng.integers(0, 256, k).astype(np.uint8)
+    b[2 * k:3 * k] = a[2 * k:3 * k] ^ 0x80
+    return a, b
+
+
+def test_comparator_rule_matches_reference(hc, ref):
+    rng = np.random.default_rng(17)
+    for dtype, bias, mode in ((abi.FP32, 0, 0), (abi.BF16, 0, 0), (abi.FP8_143, 7, 2), (abi.FP8_143, 3, 0), (abi.FP8_143, 15, 1),
+                              (abi.FP8_152, 15, 0), (abi.FP8_152, 24, 2)):
+        for cd in (1, 64, 2304, 200704):
+            a, b = comparator_pairs(dtype, rng)
+            mine = np.zeros(a.size, np.uint8)
+            hc.hc_compare(a.ctypes.data_as(C.c_void_p), b.ctypes.data_as(C.c_void_p), mine.ctypes.data_as(C.c_void_p), C.c_size_t(a.size),
+                          dtype, bias, mode, cd)
+            want = ref.compare_elements(dtype, bias, mode, cd, a, b)
+            assert (mine == want).all(), (dtype, bias, mode, cd, np.nonzero(mine != want)[0][:5])
