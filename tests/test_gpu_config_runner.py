@@ -1,0 +1,99 @@
+"""Runs tests/configs/calculator_cases.json (written in the reference's JSON test-config format) on the backend and
+replays every test on the CPU oracle with the calculator call sequence of MmeTestManager::runReference
+(mme/mme_verification/common/mme_test_manager.cpp:766-905). The two outputs are judged by the reference's own
+comparator rule, on the device (mmeb200_compare) with the test's common-dimension size; DMA tests must match bit for bit."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from intel_gaudi3_software_b200 import abi
+from intel_gaudi3_software_b200 import config_runner as cr
+from intel_gaudi3_software_b200.abi import make_tensor as T
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+CASES = os.path.join(HERE, "configs", "calculator_cases.json")
+SEED = 3
+
+
+def oracle_flow(oracle, t, tt, lfsr, poly):
+    """runReference with the oracle as the calculator; same host tensors as the backend run."""
+    op, out_role = t["operation"], tt.out_role
+    out_dtype = tt.attr[out_role][0]
+    n_out = int(np.prod(t[out_role + "Sizes"]))
+    clip = t["clippingEn"] or t["conversionRoundingMode"] in (abi.RM_SR, abi.RM_SR_NE_DNORM)
+    mme_out = np.zeros(n_out, abi.NP_DTYPE[out_dtype])
+    acc = np.zeros(n_out, np.float32)
+    acc_t = tt.tensor(out_role, acc, dtype=abi.FP32)
+    if op in cr.CONV_OPS:
+        params = abi.make_conv_params(3, t["padding"], t["strides"], t["dilation"])
+        assert oracle.conv(acc_t, tt.tensor("x"), tt.tensor("w"), tt.tensor("y"), params, op) == 0
+    else:
+        assert oracle.bgemm(acc_t, tt.tensor("x"), tt.tensor("w"), op) == 0
+    if t["maskedBgemm"]:
+        mask_acc = np.zeros(n_out, np.float32)
+        mask_t = tt.tensor(out_role, mask_acc, dtype=abi.FP32)
+        assert oracle.bgemm(mask_t, tt.tensor("xMask", sizes_key="xSizes2"), tt.tensor("wMask", sizes_key="wSizes2"), op) == 0
+        assert oracle.memory_write(acc_t, mask_t, abi.RED_ADD, 0) == 0
+    cast = abi.make_cast_params(t["conversionRoundingMode"], relu=t["reluEn"], clip_fp=clip, clip_inf_in=t["clipInfIn"],
+                                flush_denorms=t["flushDenormals"], stochastic_ftz_fp8=t["stochasticFlush"])
+    rc, _ = oracle.activation(tt.tensor(out_role, mme_out), acc_t, cast, lfsr, poly)
+    assert rc == 0
+    out_ref = tt.host[out_role].copy()
+    assert oracle.memory_write(tt.tensor(out_role, out_ref), tt.tensor(out_role, mme_out), t["reductionOp"], t["reductionRm"], clip) == 0
+    return out_ref
+
+
+def dma_expected(t, tt):
+    x = tt.host["x"].reshape(t["xSizes"][::-1])
+    if t["operation"] == abi.OP_MEMCPY:
+        return x.reshape(-1)
+    return np.ascontiguousarray(np.swapaxes(x, -1, -2)).reshape(-1)
+
+
+def test_config_cases_match_the_oracle(calc, best_oracle):
+    tests = cr.Parser(SEED).parse_file(CASES)
+    assert len(tests) == 77
+    lfsr, poly = calc.get_lfsr(256)
+    failures = []
+    for i, t in enumerate(tests):
+        if t["operation"] == abi.OP_TRANS:
+            t = dict(t, ySizes=[t["xSizes"][1], t["xSizes"][0]] + t["xSizes"][2:])
+        calc.set_lfsr(lfsr, poly)
+        got, tt = cr.run_test(calc, t)
+        if t["operation"] in cr.DMA_OPS:
+            want = dma_expected(t, tt)
+            if not (got.view(np.uint8) == want.view(np.uint8)).all():
+                failures.append((i, t["testName"], "dma bytes differ"))
+            continue
+        want = oracle_flow(best_oracle, t, tt, lfsr, poly)
+        dtype, bias, mode = tt.attr[tt.out_role]
+        sizes = t[tt.out_role + "Sizes"]
+        bad, first = calc.compare(T(got, dtype, sizes, fp_bias=bias, inf_nan_mode=mode), T(want, dtype, sizes, fp_bias=bias, inf_nan_mode=mode),
+                                  cr.common_dim_size(t))
+        if bad:
+            failures.append((i, t["testName"], cr.OP_NAMES[t["operation"]], cr.DTYPE_NAMES[dtype], bad, first,
+                             got.reshape(-1)[first].item(), want.reshape(-1)[first].item()))
+    assert not failures, failures[:10]
+
+
+def test_command_line(tmp_path):
+    env = dict(os.environ, PYTHONPATH=os.path.dirname(HERE))
+    p = subprocess.run([sys.executable, "-m", "intel_gaudi3_software_b200.config_runner", CASES, "--seed", str(SEED), "--dump", str(tmp_path)],
+                       capture_output=True, text=True, timeout=600, env=env, cwd=os.path.dirname(HERE))
+    lines = [json.loads(l) for l in p.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 77, p.stdout[-2000:] + p.stderr[-2000:]
+    # the transposes of this file keep ySizes = xSizes, which the calculator rejects like the reference's assert does
+    errors = [l for l in lines if l["status"] != "ok"]
+    assert all(l["operation"] == "transpose" for l in errors), errors[:3]
+    assert p.returncode == (1 if errors else 0)
+    assert len(os.listdir(tmp_path)) == 77 - len(errors)
+    # same seed, same bytes
+    p2 = subprocess.run([sys.executable, "-m", "intel_gaudi3_software_b200.config_runner", CASES, "--seed", str(SEED)],
+                        capture_output=True, text=True, timeout=600, env=env, cwd=os.path.dirname(HERE))
+    again = [json.loads(l) for l in p2.stdout.splitlines() if l.startswith("{")]
+    assert [l.get("crc32") for l in lines] == [l.get("crc32") for l in again]
