@@ -35,6 +35,10 @@ void hc_compare(const uint8_t* a, const uint8_t* b, uint8_t* equal, size_t n, in
         equal[i] = compare_elements(ra, rb, c) ? 1 : 0;
     }
 }
+void hc_bf16_rmw(uint16_t* mem, const uint16_t* in, size_t n, int op, int rm, int clip)
+{
+    for (size_t i = 0; i < n; i++) mem[i] = uint16_t(bf16_rmw(mem[i], in[i], op, rm, clip != 0));
+}
 int hc_fp8_foreign(uint32_t code, int exp_width, int mode) { return fp8_code_is_foreign(code, exp_width, mode); }
 uint32_t hc_lfsr(uint32_t v, uint32_t poly) { return lfsr32_step(v, poly); }
 uint32_t hc_philox(uint64_t seed, uint64_t offset, uint64_t index) { return philox_word(seed, offset, index); }

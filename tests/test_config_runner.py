@@ -20,14 +20,14 @@ def by_name(tests, name):
 
 def test_cartesian_expansion_and_defaults():
     tests = cr.Parser(3).parse_file(CASES)
-    assert len(tests) == 77
+    assert len(tests) == 85
     fwd = by_name(tests, "fwd 3x3 pad 1")
     # last multi-valued key varies fastest; shape keys never multiply
     assert [(t["outTypeFloat"], t["reluEn"]) for t in fwd] == [(abi.BF16, False), (abi.BF16, True), (abi.FP32, False), (abi.FP32, True)]
     assert fwd[0]["xSizes"] == [48, 13, 9, 1, 3] and fwd[0]["padding"] == [1, 1, 0]
     assert fwd[0]["in2TypeFloat"] == abi.BF16 and fwd[0]["conversionRoundingMode"] == 0 and fwd[0]["reductionOp"] == abi.RED_NONE
     assert set(fwd[0]["ignored"]) == {"geometry", "convPattern"}
-    assert [t["seed"] for t in tests] == list(range(3, 3 + 77))           # seed + index, as in the reference
+    assert [t["seed"] for t in tests] == list(range(3, 3 + 85))           # seed + index, as in the reference
     assert not by_name(tests, "skipped")
 
 

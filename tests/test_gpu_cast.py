@@ -137,6 +137,22 @@ def test_memory_write(calc, port):
     assert (m.view(np.uint32) == src.view(np.uint32)).all()
 
 
+def test_memory_write_bf16(calc, port):
+    from test_numerics_host import bf16_operand_pairs
+    a, b = bf16_operand_pairs(np.random.default_rng(31), 100001)
+    n = a.size
+    for op in (abi.RED_ADD, abi.RED_SUB, abi.RED_MIN, abi.RED_MAX, abi.RED_MAX_0):
+        for rm in (0, 1, 2, 3):
+            for clip in (0, 1):
+                m1, m2 = a.copy(), a.copy()
+                assert port.memory_write(T(m1, abi.BF16, [n]), T(b.copy(), abi.BF16, [n]), op, rm, clip) == 0
+                calc.do_memory_write(T(m2, abi.BF16, [n]), T(b.copy(), abi.BF16, [n]), op, rm, clip)
+                assert (m1 == m2).all(), (op, rm, clip, int((m1 != m2).sum()))
+    with pytest.raises(Exception, match="not implemented"):
+        x = np.zeros(16, np.uint8)
+        calc.do_memory_write(T(x, abi.FP8_152, [16]), T(x.copy(), abi.FP8_152, [16]), abi.RED_ADD, 0)
+
+
 def test_dma_transpose_and_copy(calc):
     rng = np.random.default_rng(4)
     a = rng.integers(0, 65536, 37 * 53 * 3).astype(np.uint16)

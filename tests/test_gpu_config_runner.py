@@ -57,7 +57,7 @@ def dma_expected(t, tt):
 
 def test_config_cases_match_the_oracle(calc, best_oracle):
     tests = cr.Parser(SEED).parse_file(CASES)
-    assert len(tests) == 77
+    assert len(tests) == 85
     lfsr, poly = calc.get_lfsr(256)
     failures = []
     for i, t in enumerate(tests):
@@ -86,12 +86,12 @@ def test_command_line(tmp_path):
     p = subprocess.run([sys.executable, "-m", "intel_gaudi3_software_b200.config_runner", CASES, "--seed", str(SEED), "--dump", str(tmp_path)],
                        capture_output=True, text=True, timeout=600, env=env, cwd=os.path.dirname(HERE))
     lines = [json.loads(l) for l in p.stdout.splitlines() if l.startswith("{")]
-    assert len(lines) == 77, p.stdout[-2000:] + p.stderr[-2000:]
+    assert len(lines) == 85, p.stdout[-2000:] + p.stderr[-2000:]
     # the transposes of this file keep ySizes = xSizes, which the calculator rejects like the reference's assert does
     errors = [l for l in lines if l["status"] != "ok"]
     assert all(l["operation"] == "transpose" for l in errors), errors[:3]
     assert p.returncode == (1 if errors else 0)
-    assert len(os.listdir(tmp_path)) == 77 - len(errors)
+    assert len(os.listdir(tmp_path)) == 85 - len(errors)
     # same seed, same bytes
     p2 = subprocess.run([sys.executable, "-m", "intel_gaudi3_software_b200.config_runner", CASES, "--seed", str(SEED)],
                         capture_output=True, text=True, timeout=600, env=env, cwd=os.path.dirname(HERE))

@@ -9,6 +9,7 @@ import numpy as np
 import pytest
 
 from intel_gaudi3_software_b200 import abi
+from intel_gaudi3_software_b200.abi import make_tensor as T
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SRC = os.path.join(ROOT, "tests", "hostcheck", "numerics_host.cpp")
@@ -148,3 +149,35 @@ def test_comparator_rule_matches_reference(hc, ref):
                           dtype, bias, mode, cd)
             want = ref.compare_elements(dtype, bias, mode, cd, a, b)
             assert (mine == want).all(), (dtype, bias, mode, cd, np.nonzero(mine != want)[0][:5])
+
+
+def bf16_operand_pairs(rng, n=300000):
+    """Random bit patterns, near-cancelling pairs, operands many binades apart, and every special value."""
+    a = rng.integers(0, 65536, n).astype(np.uint16)
+    b = rng.integers(0, 65536, n).astype(np.uint16)
+    k = n // 4
+    b[:k] = (a[:k] ^ 0x8000) + rng.integers(-3, 4, k).astype(np.uint16)                  # a - (a +- few ulps)
+    near = rng.integers(-12, 13, k)
+    b[k:2 * k] = ((a[k:2 * k].astype(np.int32) + near * 128) & 0xFFFF).astype(np.uint16)   # exponents within 12 binades
+    b[2 * k:2 * k + k // 2] = a[2 * k:2 * k + k // 2]                                        # doubling
+    special = np.array([0, 0x8000, 0x0001, 0x8001, 0x007F, 0x0080, 0x8080, 0x0081, 0x7F7F, 0xFF7F, 0x7F80, 0xFF80, 0x7FC0, 0xFFFF, 0x3F80,
+                        0xBF80, 0x7F00, 0xFF00, 0x0100, 0x8100], np.uint16)
+    sa, sb = np.meshgrid(special, special)
+    return np.concatenate([a, sa.reshape(-1)]), np.concatenate([b, sb.reshape(-1)])
+
+
+def test_bf16_memory_write_matches_reference(hc, ref):
+    rng = np.random.default_rng(23)
+    a, b = bf16_operand_pairs(rng)
+    n = a.size
+    for op in (abi.RED_ADD, abi.RED_SUB, abi.RED_MIN, abi.RED_MAX, abi.RED_MAX_0):
+        for rm in (0, 1, 2, 3):
+            for clip in (False, True):
+                if op in (abi.RED_MIN, abi.RED_MAX) and (rm or clip):
+                    continue
+                want = a.copy()
+                assert ref.memory_write(T(want, abi.BF16, [n]), T(b.copy(), abi.BF16, [n]), op, rm, clip) == 0
+                mine = a.copy()
+                hc.hc_bf16_rmw(mine.ctypes.data_as(C.c_void_p), b.ctypes.data_as(C.c_void_p), C.c_size_t(n), op, rm, int(clip))
+                bad = np.nonzero(mine != want)[0]
+                assert bad.size == 0, (op, rm, clip, bad.size, [(hex(a[i]), hex(b[i]), hex(mine[i]), hex(want[i])) for i in bad[:6]])

@@ -114,3 +114,16 @@ def test_memory_write_reductions(port, ref):
                 assert port.memory_write(T(m1, abi.FP32, [300]), T(s, abi.FP32, [300]), op, rm, clip) == 0
                 assert ref.memory_write(T(m2, abi.FP32, [300]), T(s, abi.FP32, [300]), op, rm, clip) == 0
                 assert same(m1, m2), (op, rm, clip)
+
+
+def test_memory_write_bf16_reductions(port, ref):
+    from test_numerics_host import bf16_operand_pairs
+    a, b = bf16_operand_pairs(np.random.default_rng(29), 120000)
+    n = a.size
+    for op in (abi.RED_ADD, abi.RED_SUB, abi.RED_MIN, abi.RED_MAX, abi.RED_MAX_0):
+        for rm in (0, 1, 2, 3):
+            for clip in (False, True):
+                m1, m2 = a.copy(), a.copy()
+                assert port.memory_write(T(m1, abi.BF16, [n]), T(b.copy(), abi.BF16, [n]), op, rm, clip) == 0
+                assert ref.memory_write(T(m2, abi.BF16, [n]), T(b.copy(), abi.BF16, [n]), op, rm, clip) == 0
+                assert (m1 == m2).all(), (op, rm, clip, int((m1 != m2).sum()))
