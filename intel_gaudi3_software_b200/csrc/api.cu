@@ -14,6 +14,7 @@
 #include <vector>
 
 #include "gemm_sm100.cuh"
+#include "gemm_sm100_pair.cuh"
 #include "kernels.cuh"
 #include "mme_b200.h"
 
@@ -285,6 +286,40 @@ static int launch_gemm_kernel(mmeb200_ctx* c, const GemmParams& p, unsigned grid
     return 0;
 }
 
+// CTA-pair kernel: clusters of two CTAs; the grid is the number of pairs the device can hold at once (a cluster
+// needs both its SMs inside one GPC, so this can be fewer than sm_count / 2), or the tile count if that is smaller.
+template <int KIND>
+static int launch_pair_kernel(mmeb200_ctx* c, const GemmParams& p, uint64_t tiles) {
+    auto kern = gemm_tcgen05_pair_kernel<KIND>;
+    constexpr int smem = PairSmem::kTotal;
+    static int max_pairs[16] = {};
+    int& cached = max_pairs[c->device & 15];
+    if (cached == 0) {
+        CUDA_OK(c, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof cfg);
+        cfg.gridDim = dim3(unsigned(c->sm_count) & ~1u);
+        cfg.blockDim = dim3(kGemmThreads);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        CUDA_OK(c, cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+        if (n <= 0) return c->fail(MMEB200_ERR_CUDA, "no CTA pair fits on this device");
+        cached = n;
+    }
+    unsigned pairs = unsigned(std::min<uint64_t>(tiles, uint64_t(cached)));
+    if (const char* e = getenv("MME_B200_PAIR_GRID")) pairs = std::max(1, atoi(e));
+    if (getenv("MME_B200_DEBUG")) fprintf(stderr, "pair kernel: max active clusters %d, tiles %llu, pairs %u\n", cached, (unsigned long long) tiles, pairs);
+    kern<<<pairs * 2, kGemmThreads, smem, c->stream>>>(p);
+    c->launches++;
+    CUDA_OK(c, cudaGetLastError());
+    return 0;
+}
+
 struct GemmJob {
     TmaOperand a, b;
     bool a_im2col = false;
@@ -333,7 +368,17 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     // no empty splits
     while (split > 1 && ((p.num_k_blocks + split - 1) / split) * (split - 1) >= p.num_k_blocks) --split;
     p.split_k = split;
-    p.idesc = make_instr_desc(j.a.hw_fmt, j.b.hw_fmt, j.a.mn_major, j.b.mn_major, kBlockM, block_n);
+    // CTA pairs (one 256 x 256 tile per two SMs) for plain GEMMs that have enough such tiles
+    bool use_pair = false;
+    if (const char* e = getenv("MME_B200_PAIR")) use_pair = atoi(e) != 0;                       // tuning knob
+    if (use_pair && (j.a_im2col || c->pending_peer || split != 1 || j.M < 256 || j.N < 256)) use_pair = false;
+    if (use_pair) {
+        block_n = 128;   // each CTA stages 128 of the pair's 256 columns of B
+        p.m_tiles = (j.M + 255) / 256;
+        p.n_tiles = (j.N + 255) / 256;
+    }
+    p.idesc = use_pair ? make_instr_desc(j.a.hw_fmt, j.b.hw_fmt, j.a.mn_major, j.b.mn_major, 256, 256)
+                       : make_instr_desc(j.a.hw_fmt, j.b.hw_fmt, j.a.mn_major, j.b.mn_major, kBlockM, block_n);
     p.status = c->d_status;
     p.scale = o.scale;
     p.out_dtype = o.dtype;
@@ -377,7 +422,12 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
 
     const unsigned grid = unsigned(std::min<uint64_t>(tiles * split, uint64_t(c->sm_count)));
     int rc;
-    if (block_n == 256) {
+    if (use_pair) {
+        const uint64_t pair_tiles = uint64_t(p.m_tiles) * p.n_tiles * p.batches;
+        rc = j.kind == KIND_F16 ? launch_pair_kernel<KIND_F16>(c, p, pair_tiles)
+             : j.kind == KIND_TF32 ? launch_pair_kernel<KIND_TF32>(c, p, pair_tiles)
+                                   : launch_pair_kernel<KIND_F8>(c, p, pair_tiles);
+    } else if (block_n == 256) {
         rc = j.kind == KIND_F16 ? launch_gemm_kernel<KIND_F16, 256, 4>(c, p, grid)
              : j.kind == KIND_TF32 ? launch_gemm_kernel<KIND_TF32, 256, 4>(c, p, grid)
                                    : launch_gemm_kernel<KIND_F8, 256, 4>(c, p, grid);

@@ -161,6 +161,118 @@ __device__ __forceinline__ void epilogue_convert(uint32_t (&v)[32], const GemmPa
     }
 }
 
+// Epilogue of one output tile, run by one epilogue warp for its 32 rows: reads BLOCK_N accumulator columns from
+// tensor memory (tmem_acc = the warp's lane window of the tile's accumulator), converts and stores them.
+// m0 is the first row of the CTA's 128-row block, n0 the first column.
+template <int BLOCK_N>
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t m0, uint32_t n0, uint32_t batch, uint32_t split,
+                                              uint32_t tmem_acc, uint8_t* stage_out, uint32_t& store_buf, uint32_t sub, uint32_t lane,
+                                              uint32_t out_elem) {
+    const uint32_t row = m0 + sub * 32 + lane;
+    uint32_t bi[3];
+    {
+        uint32_t b = batch;
+        bi[0] = b % p.bsz[0]; b /= p.bsz[0];
+        bi[1] = b % p.bsz[1]; b /= p.bsz[1];
+        bi[2] = b;
+    }
+    const uint64_t flat_row = (uint64_t(batch) * p.M + row) * p.N;  // index base for the random stream
+    if (p.tma_store) {
+        // ---- stage 128-byte-wide column chunks in shared memory (128-byte swizzle) and let the
+        //      copy engine write them: full-line, coalesced stores, edges clipped by the tensor map
+        const uint32_t cols_per_chunk = kRowBytes / out_elem;    // 32 fp32 / 64 bf16 / 128 fp8 columns
+        const uint32_t lds_per_chunk = cols_per_chunk / 32;
+        // each warp owns two 32-row x 128-byte buffers and issues its own stores: warps never
+        // wait for one another here
+        uint8_t* my_bufs = stage_out + sub * (2 * 32 * kRowBytes);
+        const uint32_t sw = (lane & 7);
+#pragma unroll 1
+        for (uint32_t ch = 0; ch < BLOCK_N / cols_per_chunk; ++ch) {
+            const uint32_t col0 = n0 + ch * cols_per_chunk;
+            if (col0 >= p.N) break;  // uniform over the CTA
+            uint8_t* buf = my_bufs + store_buf * (32 * kRowBytes);
+            if (lane == 0) tma_store_wait_read<1>();   // the store issued two chunks ago has drained this buffer
+            __syncwarp();
+            uint8_t* my_row = buf + lane * kRowBytes;
+#pragma unroll 1
+            for (uint32_t l = 0; l < lds_per_chunk; ++l) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(tmem_acc + ch * cols_per_chunk + l * 32, v);
+                tmem_ld_wait();
+                epilogue_convert(v, p, out_elem, flat_row + col0 + l * 32);
+                if (out_elem == 4) {
+#pragma unroll
+                    for (uint32_t q = 0; q < 8; ++q)
+                        *reinterpret_cast<uint4*>(my_row + (((l * 8 + q) ^ sw) << 4)) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                } else if (out_elem == 2) {
+#pragma unroll
+                    for (uint32_t q = 0; q < 4; ++q)
+                        *reinterpret_cast<uint4*>(my_row + (((l * 4 + q) ^ sw) << 4)) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                } else {
+#pragma unroll
+                    for (uint32_t q = 0; q < 2; ++q)
+                        *reinterpret_cast<uint4*>(my_row + (((l * 2 + q) ^ sw) << 4)) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                }
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_5d(&p.tm_out, buf, int(col0), int(m0 + sub * 32), int(bi[0]), int(bi[1]), int(bi[2]));
+                tma_store_commit();
+            }
+            store_buf ^= 1;
+        }
+    } else {
+        uint64_t base_off;
+        if (p.split_k > 1) {
+            base_off = (uint64_t(split) * p.batches + batch) * uint64_t(p.M) * p.N + uint64_t(row) * p.N;
+        } else {
+            base_off = bi[0] * p.out_bstride[0] + bi[1] * p.out_bstride[1] + bi[2] * p.out_bstride[2] + uint64_t(row) * p.out_ld;
+        }
+#pragma unroll 1
+        for (uint32_t ch = 0; ch < BLOCK_N / 32; ++ch) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(tmem_acc + ch * 32, v);
+            tmem_ld_wait();
+            const uint32_t col0 = n0 + ch * 32;
+            if (row >= p.M || col0 >= p.N) continue;
+            const uint32_t ncols = min(32u, p.N - col0);
+            uint32_t elem = 4;
+            uint8_t* dst;
+            if (p.split_k > 1) {
+                dst = reinterpret_cast<uint8_t*>(reinterpret_cast<float*>(p.out) + base_off + col0);
+            } else {
+                elem = out_elem;
+                dst = reinterpret_cast<uint8_t*>(p.out) + (base_off + col0) * out_elem;
+                epilogue_convert(v, p, out_elem, flat_row + col0);
+            }
+            // v[0 .. 8*elem) now holds 32 packed outputs
+            if (ncols == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+                if (elem == 4) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                } else if (elem == 2) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                }
+            } else {
+                // ragged edge or unaligned row: element-wise, statically indexed
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    if (uint32_t(j) < ncols) {
+                        if (elem == 4) reinterpret_cast<uint32_t*>(dst)[j] = v[j];
+                        else if (elem == 2) reinterpret_cast<uint16_t*>(dst)[j] = uint16_t(v[j / 2] >> (16 * (j & 1)));
+                        else dst[j] = uint8_t(v[j / 4] >> (8 * (j & 3)));
+                    }
+                }
+            }
+        }
+    }
+}
+
 template <int KIND, int BLOCK_N, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     using S = GemmSmem<BLOCK_N, STAGES>;
@@ -426,110 +538,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t row = tc.m0 + sub * 32 + lane;
-            uint32_t bi[3];
-            {
-                uint32_t b = tc.batch;
-                bi[0] = b % p.bsz[0]; b /= p.bsz[0];
-                bi[1] = b % p.bsz[1]; b /= p.bsz[1];
-                bi[2] = b;
-            }
-            const uint64_t flat_row = (uint64_t(tc.batch) * p.M + row) * p.N;  // index base for the random stream
             const uint32_t tmem_acc = tmem_base + acc * BLOCK_N + ((sub * 32) << 16);
-            if (p.tma_store) {
-                // ---- stage 128-byte-wide column chunks in shared memory (128-byte swizzle) and let the
-                //      copy engine write them: full-line, coalesced stores, edges clipped by the tensor map
-                const uint32_t cols_per_chunk = kRowBytes / out_elem;    // 32 fp32 / 64 bf16 / 128 fp8 columns
-                const uint32_t lds_per_chunk = cols_per_chunk / 32;
-                // each warp owns two 32-row x 128-byte buffers and issues its own stores: warps never
-                // wait for one another here
-                uint8_t* my_bufs = stage_out + sub * (2 * 32 * kRowBytes);
-                const uint32_t sw = (lane & 7);
-#pragma unroll 1
-                for (uint32_t ch = 0; ch < BLOCK_N / cols_per_chunk; ++ch) {
-                    const uint32_t col0 = n0 + ch * cols_per_chunk;
-                    if (col0 >= p.N) break;  // uniform over the CTA
-                    uint8_t* buf = my_bufs + store_buf * (32 * kRowBytes);
-                    if (lane == 0) tma_store_wait_read<1>();   // the store issued two chunks ago has drained this buffer
-                    __syncwarp();
-                    uint8_t* my_row = buf + lane * kRowBytes;
-#pragma unroll 1
-                    for (uint32_t l = 0; l < lds_per_chunk; ++l) {
-                        uint32_t v[32];
-                        tmem_ld_32x32b_x32(tmem_acc + ch * cols_per_chunk + l * 32, v);
-                        tmem_ld_wait();
-                        epilogue_convert(v, p, out_elem, flat_row + col0 + l * 32);
-                        if (out_elem == 4) {
-#pragma unroll
-                            for (uint32_t q = 0; q < 8; ++q)
-                                *reinterpret_cast<uint4*>(my_row + (((l * 8 + q) ^ sw) << 4)) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                        } else if (out_elem == 2) {
-#pragma unroll
-                            for (uint32_t q = 0; q < 4; ++q)
-                                *reinterpret_cast<uint4*>(my_row + (((l * 4 + q) ^ sw) << 4)) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                        } else {
-#pragma unroll
-                            for (uint32_t q = 0; q < 2; ++q)
-                                *reinterpret_cast<uint4*>(my_row + (((l * 2 + q) ^ sw) << 4)) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                        }
-                    }
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_store_5d(&p.tm_out, buf, int(col0), int(tc.m0 + sub * 32), int(bi[0]), int(bi[1]), int(bi[2]));
-                        tma_store_commit();
-                    }
-                    store_buf ^= 1;
-                }
-            } else {
-                uint64_t base_off;
-                if (p.split_k > 1) {
-                    base_off = (uint64_t(tc.split) * p.batches + tc.batch) * uint64_t(p.M) * p.N + uint64_t(row) * p.N;
-                } else {
-                    base_off = bi[0] * p.out_bstride[0] + bi[1] * p.out_bstride[1] + bi[2] * p.out_bstride[2] + uint64_t(row) * p.out_ld;
-                }
-#pragma unroll 1
-                for (uint32_t ch = 0; ch < BLOCK_N / 32; ++ch) {
-                    uint32_t v[32];
-                    tmem_ld_32x32b_x32(tmem_acc + ch * 32, v);
-                    tmem_ld_wait();
-                    const uint32_t col0 = n0 + ch * 32;
-                    if (row >= p.M || col0 >= p.N) continue;
-                    const uint32_t ncols = min(32u, p.N - col0);
-                    uint32_t elem = 4;
-                    uint8_t* dst;
-                    if (p.split_k > 1) {
-                        dst = reinterpret_cast<uint8_t*>(reinterpret_cast<float*>(p.out) + base_off + col0);
-                    } else {
-                        elem = out_elem;
-                        dst = reinterpret_cast<uint8_t*>(p.out) + (base_off + col0) * out_elem;
-                        epilogue_convert(v, p, out_elem, flat_row + col0);
-                    }
-                    // v[0 .. 8*elem) now holds 32 packed outputs
-                    if (ncols == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-                        if (elem == 4) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                        } else if (elem == 2) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 2; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                        }
-                    } else {
-                        // ragged edge or unaligned row: element-wise, statically indexed
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (uint32_t(j) < ncols) {
-                                if (elem == 4) reinterpret_cast<uint32_t*>(dst)[j] = v[j];
-                                else if (elem == 2) reinterpret_cast<uint16_t*>(dst)[j] = uint16_t(v[j / 2] >> (16 * (j & 1)));
-                                else dst[j] = uint8_t(v[j / 4] >> (8 * (j & 3)));
-                            }
-                        }
-                    }
-                }
-            }
+            epilogue_tile<BLOCK_N>(p, tc.m0, n0, tc.batch, tc.split, tmem_acc, stage_out, store_buf, sub, lane, out_elem);
             tc_fence_before_sync();
             mbar_arrive(&tmem_empty_bar[acc]);
             acc ^= 1;

@@ -1,0 +1,215 @@
+// CTA-pair variant of the tcgen05 GEMM (plain tiled operands, no split-K): two CTAs of one cluster
+// compute one 256 x 256 output tile with a single tcgen05.mma.cta_group::2 per 32 bytes of K. Each CTA
+// stages its own 128 rows of A and only its half of B (128 of the tile's 256 columns), so a stage is
+// 32 KB instead of 48 KB: B's shared-memory traffic halves and the ring gets 6 stages.
+//
+// Roles per CTA are the same as in gemm_tcgen05_kernel, with these differences:
+//   * full[stage] lives in the even-ranked ("leader") CTA. Its two arrivals are the leader's A and B
+//     producer, each announcing the bytes of BOTH CTAs' loads of that operand; the partner's
+//     producers only issue their loads, which complete on the leader's barrier
+//     (cp.async.bulk.tensor ... cta_group::2, no multicast). The partner never makes a remote
+//     arrival per stage: a release-ordered remote arrival costs a round trip between the SMs.
+//   * only the leader's MMA thread issues; its commits arrive on empty[stage] / tmem_full[acc] of
+//     BOTH CTAs (tcgen05.commit ... multicast::cluster).
+//   * tmem_empty[acc] lives in the leader and counts one arrival per epilogue warp of both CTAs.
+//   * tensor memory is allocated and freed by one warp of each CTA with the cta_group::2 forms; the
+//     cluster synchronises after set-up and before tear-down.
+// Every wait is bounded as in the single-CTA kernel; after a wait gives up each role leaves its loop,
+// and all threads still meet at the final cluster barrier.
+#pragma once
+#include "gemm_sm100.cuh"
+
+namespace mmeb200 {
+
+constexpr int kPairStages = 6;
+constexpr int kPairBlockN = 256;       // columns of the pair's tile; each CTA stages half of them
+
+struct PairSmem {
+    static constexpr int kABytes = kBlockM * kRowBytes;
+    static constexpr int kBBytes = (kPairBlockN / 2) * kRowBytes;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kBarrierBytes = 1024;
+    static constexpr int kOutStageBytes = 2 * kBlockM * kRowBytes;
+    static constexpr int kTotal = kPairStages * kStageBytes + kBarrierBytes + kOutStageBytes + 1024;
+};
+
+// p.m_tiles counts 256-row tiles here; p.n_tiles counts 256-column tiles; p.split_k == 1; p.a_mode == A_TILED.
+template <int KIND>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_pair_kernel(const __grid_constant__ GemmParams p) {
+    using S = PairSmem;
+    constexpr int STAGES = kPairStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * S::kStageBytes);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* tmem_full_bar = empty_bar + STAGES;
+    uint64_t* tmem_empty_bar = tmem_full_bar + 2;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();          // 0 = leader
+    const uint32_t pair = blockIdx.x >> 1;
+    const uint32_t num_pairs = gridDim.x >> 1;
+    const uint32_t total_tiles = p.m_tiles * p.n_tiles * p.batches;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 2);    // the leader's A and B producer (used in the leader only)
+            mbar_init(&empty_bar[s], 1);   // one multicast commit
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tmem_full_bar[b], 1);
+            mbar_init(&tmem_empty_bar[b], 8);  // four epilogue warps of both CTAs (used in the leader only)
+        }
+        fence_mbar_init();
+        tma_prefetch_desc(&p.tm_a);
+        tma_prefetch_desc(&p.tm_b);
+        if (p.tma_store) tma_prefetch_desc(&p.tm_out);
+    }
+    if (warp == 2) {
+        tmem_alloc_pair(tmem_holder, 2 * kPairBlockN);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    cluster_sync_all();      // both CTAs' barriers are initialised and both allocations are done
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 0 || warp == 3) {
+        // ------------------------------------------------------------------ TMA producers (warp 0: A, warp 3: B)
+        if (elect_one()) {
+            const bool is_a = warp == 0;
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            const bool mn = (is_a ? p.a_mn_major : p.b_mn_major) != 0;
+            const CUtensorMap* map = is_a ? &p.tm_a : &p.tm_b;
+            const uint32_t* bcast = is_a ? p.a_bcast : p.b_bcast;
+            const uint32_t groups = mn ? (kBlockM * p.elem_bytes) / kRowBytes : 1;   // 128 rows or columns either way
+            const uint32_t mn_group_elems = kRowBytes / p.elem_bytes;
+            const uint32_t mn_group_bytes = p.block_k * kRowBytes;
+            const uint32_t block_k = p.block_k;
+            const uint32_t my_bytes = is_a ? uint32_t(S::kABytes) : uint32_t(S::kBBytes);
+            const uint32_t dst_off = is_a ? 0u : uint32_t(S::kABytes);
+            const uint32_t full0 = mapa_shared(smem_u32(&full_bar[0]), 0);   // the leader's full[0]
+            for (uint32_t t = pair; t < total_tiles && ok; t += num_pairs) {
+                const TileCoord tc = decode_tile(p, t);
+                // first row (A) or column (B) this CTA stages
+                const uint32_t mn0 = is_a ? tc.m0 * 2 + rank * kBlockM : tc.n0 * kPairBlockN + rank * (kPairBlockN / 2);
+                uint32_t bi[3];
+                {
+                    uint32_t b = tc.batch;
+                    bi[0] = b % p.bsz[0]; b /= p.bsz[0];
+                    bi[1] = b % p.bsz[1]; b /= p.bsz[1];
+                    bi[2] = b;
+                }
+                const int c2 = bcast[0] ? 0 : bi[0], c3 = bcast[1] ? 0 : bi[1], c4 = bcast[2] ? 0 : bi[2];
+                uint32_t k_elem = 0;
+                for (uint32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+                    if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, kWaitLimitNs)) {
+                        atomicCAS(p.status, 0u, WAIT_PRODUCER_EMPTY);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* dst = smem + stage * S::kStageBytes + dst_off;
+                    const uint32_t bar = full0 + stage * 8;
+                    if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * my_bytes);   // this CTA's bytes and the partner's
+                    if (!mn) {
+                        tma_load_5d_pair(dst, map, bar, int(k_elem), int(mn0), c2, c3, c4);
+                    } else {
+#pragma unroll
+                        for (uint32_t g = 0; g < 4; ++g)
+                            if (g < groups) tma_load_5d_pair(dst + g * mn_group_bytes, map, bar, int(mn0 + g * mn_group_elems), int(k_elem), c2, c3, c4);
+                    }
+                    k_elem += block_k;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (rank == 0 && elect_one()) {
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            const uint32_t mn_k_step = (kUmmaKBytes / p.elem_bytes) * kRowBytes;
+            const uint32_t mn_lbo = p.block_k * kRowBytes;
+            const uint32_t smem_base = smem_u32(smem);
+            const uint64_t a_desc0 = p.a_mn_major ? make_smem_desc(smem_base, mn_lbo, 1024) : make_smem_desc(smem_base, 16, 1024);
+            const uint64_t b_desc0 = p.b_mn_major ? make_smem_desc(smem_base + S::kABytes, mn_lbo, 1024)
+                                                  : make_smem_desc(smem_base + S::kABytes, 16, 1024);
+            const uint64_t a_step = (p.a_mn_major ? mn_k_step : uint32_t(kUmmaKBytes)) >> 4;
+            const uint64_t b_step = (p.b_mn_major ? mn_k_step : uint32_t(kUmmaKBytes)) >> 4;
+            constexpr uint64_t kStageUnits = S::kStageBytes >> 4;
+            const uint32_t idesc = p.idesc;   // M = 256, N = 256
+            for (uint32_t t = pair; t < total_tiles && ok; t += num_pairs) {
+                if (!mbar_wait_bounded(&tmem_empty_bar[acc], acc_phase ^ 1, kWaitLimitNs)) {
+                    atomicCAS(p.status, 0u, WAIT_MMA_TMEM_EMPTY);
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * kPairBlockN;
+                uint32_t accumulate = 0;
+                for (uint32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+                    if (!mbar_wait_bounded(&full_bar[stage], phase, kWaitLimitNs)) {
+                        atomicCAS(p.status, 0u, WAIT_MMA_FULL);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint64_t a_desc = a_desc0 + stage * kStageUnits;
+                    const uint64_t b_desc = b_desc0 + stage * kStageUnits;
+#pragma unroll
+                    for (uint32_t k = 0; k < kRowBytes / kUmmaKBytes; ++k) {
+                        umma_ss_pair<KIND>(d_tmem, a_desc + k * a_step, b_desc + k * b_step, idesc, accumulate);
+                        accumulate = 1;
+                    }
+                    umma_commit_pair(&empty_bar[stage], 3);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit_pair(&tmem_full_bar[acc], 3);
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1;
+            }
+        }
+        __syncwarp();
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+        const uint32_t sub = warp & 3;
+        uint32_t acc = 0, acc_phase = 0;
+        const uint32_t out_elem = dtype_size(int(p.out_dtype));
+        uint8_t* stage_out = smem + STAGES * S::kStageBytes + S::kBarrierBytes;
+        uint32_t store_buf = 0;
+        const uint32_t leader_tmem_empty = mapa_shared(smem_u32(&tmem_empty_bar[0]), 0);
+        for (uint32_t t = pair; t < total_tiles; t += num_pairs) {
+            const TileCoord tc = decode_tile(p, t);
+            bool ready = mbar_wait_bounded(&tmem_full_bar[acc], acc_phase, kWaitLimitNs);
+            ready = __all_sync(0xffffffffu, ready);
+            if (!ready) {
+                atomicCAS(p.status, 0u, WAIT_EPILOGUE_TMEM_FULL);
+                break;
+            }
+            tc_fence_after_sync();
+            const uint32_t tmem_acc = tmem_base + acc * kPairBlockN + ((sub * 32) << 16);
+            epilogue_tile<kPairBlockN>(p, tc.m0 * 2 + rank * kBlockM, tc.n0 * kPairBlockN, tc.batch, 0, tmem_acc, stage_out, store_buf, sub,
+                                       lane, out_elem);
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_tmem_empty + acc * 8);
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1;
+        }
+        if (p.tma_store && lane == 0) tma_store_wait_all<0>();
+    }
+
+    // nobody may leave (or free tensor memory) while the partner can still signal this CTA's barriers or read its operands
+    tc_fence_before_sync();
+    cluster_sync_all();
+    if (warp == 2) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, 2 * kPairBlockN);
+    }
+}
+
+}  // namespace mmeb200
