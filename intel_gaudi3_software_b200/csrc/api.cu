@@ -351,32 +351,35 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     p.b_mn_major = j.b.mn_major;
     p.a_mode = j.a_im2col ? A_IM2COL : A_TILED;
     p.conv = j.conv;
-    // tile width: 256 columns whenever the problem has them (half the operand traffic per FLOP of a
-    // 128-wide tile); split-K below fills the machine when that leaves few tiles
+    // Tile geometry. CTA pairs (one 256 x 256 tile per two SMs, half the B traffic per SM) whenever the
+    // problem is at least one such tile; else 128 x 256 tiles per CTA whenever N has the columns; else
+    // 128 x 128. Split-K below fills the machine when that leaves few tiles.
+    bool use_pair = j.M >= 256 && j.N >= 256 && !c->pending_peer;
+    if (const char* e = getenv("MME_B200_PAIR")) use_pair = use_pair && atoi(e) != 0;            // tuning knob
     const bool wide = j.N > 128;
     int block_n = wide ? 256 : 128;
-    if (const char* e = getenv("MME_B200_BLOCK_N")) block_n = atoi(e) == 256 ? 256 : 128;   // tuning knob
-    p.n_tiles = (j.N + block_n - 1) / block_n;
-    const uint64_t tiles = uint64_t(p.m_tiles) * p.n_tiles * p.batches;
+    if (const char* e = getenv("MME_B200_BLOCK_N")) { block_n = atoi(e) == 256 ? 256 : 128; use_pair = false; }   // tuning knob
+    uint64_t tiles, units;   // units = CTAs or CTA pairs the device runs at once
+    if (use_pair) {
+        p.m_tiles = (j.M + 255) / 256;
+        p.n_tiles = (j.N + 255) / 256;
+        block_n = 128;       // each CTA stages 128 of the pair's 256 columns of B
+        units = uint64_t(c->sm_count) / 2;
+    } else {
+        p.n_tiles = (j.N + block_n - 1) / block_n;
+        units = uint64_t(c->sm_count);
+    }
+    tiles = uint64_t(p.m_tiles) * p.n_tiles * p.batches;
     uint32_t split = 1;
     if (const char* e = getenv("MME_B200_SPLIT_K")) j.force_split = atoi(e);                   // tuning knob
     if (j.force_split > 0) split = std::min<uint32_t>(j.force_split, p.num_k_blocks);
-    else if (tiles * 2 <= uint64_t(c->sm_count) && p.num_k_blocks >= 8) {
-        split = uint32_t(std::min<uint64_t>(c->sm_count / tiles, p.num_k_blocks / 4));
+    else if (tiles * 2 <= units && p.num_k_blocks >= 8) {
+        split = uint32_t(std::min<uint64_t>(units / tiles, p.num_k_blocks / 4));
         split = std::max(1u, std::min(split, 64u));
     }
     // no empty splits
     while (split > 1 && ((p.num_k_blocks + split - 1) / split) * (split - 1) >= p.num_k_blocks) --split;
     p.split_k = split;
-    // CTA pairs (one 256 x 256 tile per two SMs) for plain GEMMs that have enough such tiles
-    bool use_pair = false;
-    if (const char* e = getenv("MME_B200_PAIR")) use_pair = atoi(e) != 0;                       // tuning knob
-    if (use_pair && (j.a_im2col || c->pending_peer || split != 1 || j.M < 256 || j.N < 256)) use_pair = false;
-    if (use_pair) {
-        block_n = 128;   // each CTA stages 128 of the pair's 256 columns of B
-        p.m_tiles = (j.M + 255) / 256;
-        p.n_tiles = (j.N + 255) / 256;
-    }
     p.idesc = use_pair ? make_instr_desc(j.a.hw_fmt, j.b.hw_fmt, j.a.mn_major, j.b.mn_major, 256, 256)
                        : make_instr_desc(j.a.hw_fmt, j.b.hw_fmt, j.a.mn_major, j.b.mn_major, kBlockM, block_n);
     p.status = c->d_status;
@@ -423,7 +426,7 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     const unsigned grid = unsigned(std::min<uint64_t>(tiles * split, uint64_t(c->sm_count)));
     int rc;
     if (use_pair) {
-        const uint64_t pair_tiles = uint64_t(p.m_tiles) * p.n_tiles * p.batches;
+        const uint64_t pair_tiles = tiles * split;
         rc = j.kind == KIND_F16 ? launch_pair_kernel<KIND_F16>(c, p, pair_tiles)
              : j.kind == KIND_TF32 ? launch_pair_kernel<KIND_TF32>(c, p, pair_tiles)
                                    : launch_pair_kernel<KIND_F8>(c, p, pair_tiles);

@@ -161,6 +161,171 @@ __device__ __forceinline__ void epilogue_convert(uint32_t (&v)[32], const GemmPa
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Operand feeds: the coordinate bookkeeping of the two TMA producer threads, shared by the
+// single-CTA and the CTA-pair kernel (PAIR selects the load form whose completion may be signalled
+// on the partner CTA's barrier). Everything that is constant inside a tile is computed in
+// begin_tile; coordinates then advance incrementally, with no division per k block.
+// ---------------------------------------------------------------------------------------------
+template <bool PAIR>
+__device__ __forceinline__ void feed_load_tiled(void* dst, const CUtensorMap* m, uint32_t bar, int c0, int c1, int c2, int c3, int c4) {
+    if constexpr (PAIR) tma_load_5d_pair(dst, m, bar, c0, c1, c2, c3, c4);
+    else tma_load_5d(dst, m, bar, c0, c1, c2, c3, c4);
+}
+template <bool PAIR>
+__device__ __forceinline__ void feed_load_im2col(void* dst, const CUtensorMap* m, uint32_t bar, int c, int w, int h, int n, uint16_t ow,
+                                                 uint16_t oh) {
+    if constexpr (PAIR) tma_load_im2col_4d_pair(dst, m, bar, c, w, h, n, ow, oh);
+    else tma_load_im2col_4d(dst, m, bar, c, w, h, n, ow, oh);
+}
+
+// A operand: 128 rows (or, MN-major, 128 columns of the stored matrix) starting at m0.
+struct AFeed {
+    bool a_mn, im2col, pix_k;
+    uint32_t a_groups, mn_group_elems, mn_group_bytes, block_k;
+    uint32_t m0;
+    int ab0, ab1, ab2;
+    uint32_t k_elem;                           // K coordinate of a plain (tiled) operand
+    int pw, ph, pn;                            // fwd / dedx: base position of the tile's first pixel
+    uint32_t tap_s, tap_r, k_in_tap;           // fwd / dedx: filter tap and channel offset
+    uint32_t pq, pp, pimg;                     // dedw: pixel position of the k block
+    uint16_t g_off_w[4], g_off_h[4];
+    int g_c[4];
+
+    __device__ __forceinline__ void setup(const GemmParams& p) {
+        a_mn = p.a_mn_major != 0;
+        im2col = p.a_mode == A_IM2COL;
+        pix_k = im2col && p.conv.pixels_along_k;
+        a_groups = a_mn ? (kBlockM * p.elem_bytes) / kRowBytes : 1;   // <= 4
+        mn_group_elems = kRowBytes / p.elem_bytes;
+        mn_group_bytes = p.block_k * kRowBytes;
+        block_k = p.block_k;
+    }
+    __device__ __forceinline__ void begin_tile(const GemmParams& p, uint32_t first_row, uint32_t batch, uint32_t kb_begin) {
+        m0 = first_row;
+        uint32_t b = batch;
+        const uint32_t i0 = b % p.bsz[0]; b /= p.bsz[0];
+        const uint32_t i1 = b % p.bsz[1]; b /= p.bsz[1];
+        ab0 = p.a_bcast[0] ? 0 : int(i0);
+        ab1 = p.a_bcast[1] ? 0 : int(i1);
+        ab2 = p.a_bcast[2] ? 0 : int(b);
+        k_elem = kb_begin * block_k;
+        pw = ph = pn = 0;
+        tap_s = tap_r = k_in_tap = 0;
+        pq = pp = pimg = 0;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) { g_off_w[g] = 0; g_off_h[g] = 0; g_c[g] = 0; }
+        if (im2col && !pix_k) {
+            const uint32_t q = m0 % p.conv.out_w;
+            const uint32_t rest = m0 / p.conv.out_w;
+            pw = int(q) * p.conv.stride_w + p.conv.lower_w;
+            ph = int(rest % p.conv.out_h) * p.conv.stride_h + p.conv.lower_h;
+            pn = int(rest / p.conv.out_h);
+            const uint32_t tap = kb_begin / p.conv.k_blocks_per_tap;
+            k_in_tap = (kb_begin % p.conv.k_blocks_per_tap) * block_k;
+            tap_s = tap % p.conv.taps_w;
+            tap_r = tap / p.conv.taps_w;
+        } else if (pix_k) {
+            const uint32_t pix = kb_begin * block_k;
+            pq = pix % p.conv.out_w;
+            const uint32_t rest = pix / p.conv.out_w;
+            pp = rest % p.conv.out_h;
+            pimg = rest / p.conv.out_h;
+#pragma unroll
+            for (uint32_t g = 0; g < 4; ++g) {
+                if (g < a_groups) {
+                    const uint32_t m = m0 + g * mn_group_elems;
+                    const uint32_t tp = m / p.conv.channels;
+                    g_c[g] = int(m % p.conv.channels);
+                    g_off_w[g] = uint16_t((tp % p.conv.taps_w) * p.conv.dil_w);
+                    g_off_h[g] = uint16_t((tp / p.conv.taps_w) * p.conv.dil_h);
+                }
+            }
+        }
+    }
+    // issues the loads of one k block into a_dst, completion on `bar`, and steps to the next k block
+    template <bool PAIR>
+    __device__ __forceinline__ void load(const GemmParams& p, uint8_t* a_dst, uint32_t bar) {
+        if (!im2col) {
+            if (!a_mn) {
+                feed_load_tiled<PAIR>(a_dst, &p.tm_a, bar, int(k_elem), int(m0), ab0, ab1, ab2);
+            } else {
+#pragma unroll
+                for (uint32_t g = 0; g < 4; ++g)
+                    if (g < a_groups) feed_load_tiled<PAIR>(a_dst + g * mn_group_bytes, &p.tm_a, bar, int(m0 + g * mn_group_elems), int(k_elem), ab0, ab1, ab2);
+            }
+            k_elem += block_k;
+        } else if (!pix_k) {
+            const uint32_t s = p.conv.flip ? p.conv.taps_w - 1 - tap_s : tap_s;
+            const uint32_t r = p.conv.flip ? p.conv.taps_h - 1 - tap_r : tap_r;
+            feed_load_im2col<PAIR>(a_dst, &p.tm_a, bar, int(k_in_tap), pw, ph, pn, uint16_t(s * p.conv.dil_w), uint16_t(r * p.conv.dil_h));
+            k_in_tap += block_k;
+            if (k_in_tap >= uint32_t(p.conv.k_blocks_per_tap) * block_k) {
+                k_in_tap = 0;
+                if (++tap_s == uint32_t(p.conv.taps_w)) { tap_s = 0; ++tap_r; }
+            }
+        } else {
+            const int w0 = int(pq) * p.conv.stride_w + p.conv.lower_w;
+            const int h0 = int(pp) * p.conv.stride_h + p.conv.lower_h;
+#pragma unroll
+            for (uint32_t g = 0; g < 4; ++g)
+                if (g < a_groups) feed_load_im2col<PAIR>(a_dst + g * mn_group_bytes, &p.tm_a, bar, g_c[g], w0, h0, int(pimg), g_off_w[g], g_off_h[g]);
+            pq += block_k;
+            while (pq >= uint32_t(p.conv.out_w)) {
+                pq -= p.conv.out_w;
+                if (++pp == uint32_t(p.conv.out_h)) { pp = 0; ++pimg; }
+            }
+        }
+    }
+};
+
+// B operand: COLS columns of the output (rows of the stored K-major matrix) starting at n_first.
+template <int COLS>
+struct BFeed {
+    bool b_mn, tap_local;
+    uint32_t b_groups, mn_group_elems, mn_group_bytes, block_k;
+    uint32_t n_first, row, k_elem, k_wrap;
+    int bb0, bb1, bb2;
+
+    __device__ __forceinline__ void setup(const GemmParams& p) {
+        b_mn = p.b_mn_major != 0;
+        tap_local = p.conv.b_tap_local != 0;
+        b_groups = b_mn ? (COLS * p.elem_bytes) / kRowBytes : 1;   // <= 8
+        mn_group_elems = kRowBytes / p.elem_bytes;
+        mn_group_bytes = p.block_k * kRowBytes;
+        block_k = p.block_k;
+    }
+    __device__ __forceinline__ void begin_tile(const GemmParams& p, uint32_t first_col, uint32_t batch, uint32_t kb_begin) {
+        n_first = first_col;
+        uint32_t b = batch;
+        const uint32_t i0 = b % p.bsz[0]; b /= p.bsz[0];
+        const uint32_t i1 = b % p.bsz[1]; b /= p.bsz[1];
+        bb0 = p.b_bcast[0] ? 0 : int(i0);
+        bb1 = p.b_bcast[1] ? 0 : int(i1);
+        bb2 = p.b_bcast[2] ? 0 : int(b);
+        k_elem = kb_begin * block_k;
+        row = n_first;
+        if (tap_local) {  // dedx: B's K coordinate restarts at every filter tap, its rows move on by C
+            const uint32_t tap = kb_begin / p.conv.k_blocks_per_tap;
+            k_elem = (kb_begin % p.conv.k_blocks_per_tap) * block_k;
+            row = n_first + tap * p.conv.b_tap_rows;
+        }
+        k_wrap = tap_local ? uint32_t(p.conv.k_blocks_per_tap) * block_k : 0xFFFFFFFFu;
+    }
+    template <bool PAIR>
+    __device__ __forceinline__ void load(const GemmParams& p, uint8_t* b_dst, uint32_t bar) {
+        if (!b_mn) {
+            feed_load_tiled<PAIR>(b_dst, &p.tm_b, bar, int(k_elem), int(row), bb0, bb1, bb2);
+        } else {
+#pragma unroll
+            for (uint32_t g = 0; g < 8; ++g)
+                if (g < b_groups) feed_load_tiled<PAIR>(b_dst + g * mn_group_bytes, &p.tm_b, bar, int(n_first + g * mn_group_elems), int(k_elem), bb0, bb1, bb2);
+        }
+        k_elem += block_k;
+        if (k_elem >= k_wrap) { k_elem = 0; row += p.conv.b_tap_rows; }
+    }
+};
+
 // Epilogue of one output tile, run by one epilogue warp for its 32 rows: reads BLOCK_N accumulator columns from
 // tensor memory (tmem_acc = the warp's lane window of the tile's accumulator), converts and stores them.
 // m0 is the first row of the CTA's 128-row block, n0 the first column.
@@ -319,99 +484,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
         if (elect_one()) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            const bool a_mn = p.a_mn_major != 0;
-            const bool im2col = p.a_mode == A_IM2COL;
-            const bool pix_k = im2col && p.conv.pixels_along_k;
-            const uint32_t a_groups = a_mn ? (kBlockM * p.elem_bytes) / kRowBytes : 1;   // <= 4
-            const uint32_t mn_group_elems = kRowBytes / p.elem_bytes;
-            const uint32_t mn_group_bytes = p.block_k * kRowBytes;
-            const uint32_t block_k = p.block_k;
+            AFeed feed;
+            feed.setup(p);
             for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const TileCoord tc = decode_tile(p, t);
-                uint32_t bi[3];
-                {
-                    uint32_t b = tc.batch;
-                    bi[0] = b % p.bsz[0]; b /= p.bsz[0];
-                    bi[1] = b % p.bsz[1]; b /= p.bsz[1];
-                    bi[2] = b;
-                }
-                const int ab0 = p.a_bcast[0] ? 0 : bi[0], ab1 = p.a_bcast[1] ? 0 : bi[1], ab2 = p.a_bcast[2] ? 0 : bi[2];
-                uint32_t k_elem = tc.kb_begin * block_k;   // K coordinate of a plain (tiled) operand
-                // ---- per-tile im2col state
-                int pw = 0, ph = 0, pn = 0;                // base position of the tile's first pixel (fwd / dedx)
-                uint32_t tap_s = 0, tap_r = 0, k_in_tap = 0;            // fwd / dedx: filter tap and channel offset
-                uint32_t pq = 0, pp = 0, pimg = 0;         // dedw: pixel position of the k block
-                uint16_t g_off_w[4] = {0, 0, 0, 0}, g_off_h[4] = {0, 0, 0, 0};
-                int g_c[4] = {0, 0, 0, 0};
-                if (im2col && !pix_k) {
-                    const uint32_t q = tc.m0 % p.conv.out_w;
-                    const uint32_t rest = tc.m0 / p.conv.out_w;
-                    pw = int(q) * p.conv.stride_w + p.conv.lower_w;
-                    ph = int(rest % p.conv.out_h) * p.conv.stride_h + p.conv.lower_h;
-                    pn = int(rest / p.conv.out_h);
-                    const uint32_t tap = tc.kb_begin / p.conv.k_blocks_per_tap;
-                    k_in_tap = (tc.kb_begin % p.conv.k_blocks_per_tap) * block_k;
-                    tap_s = tap % p.conv.taps_w;
-                    tap_r = tap / p.conv.taps_w;
-                } else if (pix_k) {
-                    const uint32_t pix = tc.kb_begin * block_k;
-                    pq = pix % p.conv.out_w;
-                    const uint32_t rest = pix / p.conv.out_w;
-                    pp = rest % p.conv.out_h;
-                    pimg = rest / p.conv.out_h;
-#pragma unroll
-                    for (uint32_t g = 0; g < 4; ++g) {
-                        if (g < a_groups) {
-                            const uint32_t m = tc.m0 + g * mn_group_elems;
-                            const uint32_t tp = m / p.conv.channels;
-                            g_c[g] = int(m % p.conv.channels);
-                            g_off_w[g] = uint16_t((tp % p.conv.taps_w) * p.conv.dil_w);
-                            g_off_h[g] = uint16_t((tp / p.conv.taps_w) * p.conv.dil_h);
-                        }
-                    }
-                }
+                feed.begin_tile(p, tc.m0, tc.batch, tc.kb_begin);
                 for (uint32_t kb = tc.kb_begin; kb < tc.kb_end; ++kb) {
                     if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, kWaitLimitNs)) {
                         atomicCAS(p.status, 0u, WAIT_PRODUCER_EMPTY);
                         ok = false;
                         break;
                     }
-                    uint8_t* a_dst = smem + stage * S::kStageBytes;
-                    uint64_t* bar = &full_bar[stage];
-                    mbar_arrive_expect_tx(bar, S::kABytes);
-                    if (!im2col) {
-                        if (!a_mn) {
-                            tma_load_5d(a_dst, &p.tm_a, bar, k_elem, tc.m0, ab0, ab1, ab2);
-                        } else {
-#pragma unroll
-                            for (uint32_t g = 0; g < 4; ++g)
-                                if (g < a_groups)
-                                    tma_load_5d(a_dst + g * mn_group_bytes, &p.tm_a, bar, tc.m0 + g * mn_group_elems, k_elem, ab0, ab1, ab2);
-                        }
-                        k_elem += block_k;
-                    } else if (!pix_k) {
-                        const uint32_t s = p.conv.flip ? p.conv.taps_w - 1 - tap_s : tap_s;
-                        const uint32_t r = p.conv.flip ? p.conv.taps_h - 1 - tap_r : tap_r;
-                        tma_load_im2col_4d(a_dst, &p.tm_a, bar, int(k_in_tap), pw, ph, pn, uint16_t(s * p.conv.dil_w),
-                                           uint16_t(r * p.conv.dil_h));
-                        k_in_tap += block_k;
-                        if (k_in_tap >= uint32_t(p.conv.k_blocks_per_tap) * block_k) {
-                            k_in_tap = 0;
-                            if (++tap_s == uint32_t(p.conv.taps_w)) { tap_s = 0; ++tap_r; }
-                        }
-                    } else {
-                        const int w0 = int(pq) * p.conv.stride_w + p.conv.lower_w;
-                        const int h0 = int(pp) * p.conv.stride_h + p.conv.lower_h;
-#pragma unroll
-                        for (uint32_t g = 0; g < 4; ++g)
-                            if (g < a_groups)
-                                tma_load_im2col_4d(a_dst + g * mn_group_bytes, &p.tm_a, bar, g_c[g], w0, h0, int(pimg), g_off_w[g], g_off_h[g]);
-                        pq += block_k;
-                        while (pq >= uint32_t(p.conv.out_w)) {
-                            pq -= p.conv.out_w;
-                            if (++pp == uint32_t(p.conv.out_h)) { pp = 0; ++pimg; }
-                        }
-                    }
+                    mbar_arrive_expect_tx(&full_bar[stage], S::kABytes);
+                    feed.load<false>(p, smem + stage * S::kStageBytes, smem_u32(&full_bar[stage]));
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -422,50 +507,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
         if (elect_one()) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            const bool b_mn = p.b_mn_major != 0;
-            const bool tap_local = p.conv.b_tap_local != 0;
-            const uint32_t b_groups = b_mn ? (BLOCK_N * p.elem_bytes) / kRowBytes : 1;   // <= 8
-            const uint32_t mn_group_elems = kRowBytes / p.elem_bytes;
-            const uint32_t mn_group_bytes = p.block_k * kRowBytes;
-            const uint32_t block_k = p.block_k;
+            BFeed<BLOCK_N> feed;
+            feed.setup(p);
             for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const TileCoord tc = decode_tile(p, t);
-                const uint32_t n0 = tc.n0 * BLOCK_N;
-                uint32_t bi[3];
-                {
-                    uint32_t b = tc.batch;
-                    bi[0] = b % p.bsz[0]; b /= p.bsz[0];
-                    bi[1] = b % p.bsz[1]; b /= p.bsz[1];
-                    bi[2] = b;
-                }
-                const int bb0 = p.b_bcast[0] ? 0 : bi[0], bb1 = p.b_bcast[1] ? 0 : bi[1], bb2 = p.b_bcast[2] ? 0 : bi[2];
-                uint32_t k_elem = tc.kb_begin * block_k;
-                uint32_t row = n0;
-                if (tap_local) {  // dedx: B's K coordinate restarts at every filter tap, its rows move on by C
-                    const uint32_t tap = tc.kb_begin / p.conv.k_blocks_per_tap;
-                    k_elem = (tc.kb_begin % p.conv.k_blocks_per_tap) * block_k;
-                    row = n0 + tap * p.conv.b_tap_rows;
-                }
-                const uint32_t k_wrap = tap_local ? uint32_t(p.conv.k_blocks_per_tap) * block_k : 0xFFFFFFFFu;
+                feed.begin_tile(p, tc.n0 * BLOCK_N, tc.batch, tc.kb_begin);
                 for (uint32_t kb = tc.kb_begin; kb < tc.kb_end; ++kb) {
                     if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, kWaitLimitNs)) {
                         atomicCAS(p.status, 0u, WAIT_PRODUCER_EMPTY);
                         ok = false;
                         break;
                     }
-                    uint8_t* b_dst = smem + stage * S::kStageBytes + S::kABytes;
-                    uint64_t* bar = &full_bar[stage];
-                    mbar_arrive_expect_tx(bar, S::kBBytes);
-                    if (!b_mn) {
-                        tma_load_5d(b_dst, &p.tm_b, bar, k_elem, row, bb0, bb1, bb2);
-                    } else {
-#pragma unroll
-                        for (uint32_t g = 0; g < 8; ++g)
-                            if (g < b_groups)
-                                tma_load_5d(b_dst + g * mn_group_bytes, &p.tm_b, bar, n0 + g * mn_group_elems, k_elem, bb0, bb1, bb2);
-                    }
-                    k_elem += block_k;
-                    if (k_elem >= k_wrap) { k_elem = 0; row += p.conv.b_tap_rows; }
+                    mbar_arrive_expect_tx(&full_bar[stage], S::kBBytes);
+                    feed.load<false>(p, smem + stage * S::kStageBytes + S::kABytes, smem_u32(&full_bar[stage]));
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }

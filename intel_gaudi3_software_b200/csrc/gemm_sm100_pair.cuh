@@ -1,4 +1,4 @@
-// CTA-pair variant of the tcgen05 GEMM (plain tiled operands, no split-K): two CTAs of one cluster
+// CTA-pair variant of the tcgen05 GEMM (tiled and im2col operands, optional split-K): two CTAs of one cluster
 // compute one 256 x 256 output tile with a single tcgen05.mma.cta_group::2 per 32 bytes of K. Each CTA
 // stages its own 128 rows of A and only its half of B (128 of the tile's 256 columns), so a stage is
 // 32 KB instead of 48 KB: B's shared-memory traffic halves and the ring gets 6 stages.
@@ -33,7 +33,7 @@ struct PairSmem {
     static constexpr int kTotal = kPairStages * kStageBytes + kBarrierBytes + kOutStageBytes + 1024;
 };
 
-// p.m_tiles counts 256-row tiles here; p.n_tiles counts 256-column tiles; p.split_k == 1; p.a_mode == A_TILED.
+// p.m_tiles counts 256-row tiles here; p.n_tiles counts 256-column tiles.
 template <int KIND>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_pair_kernel(const __grid_constant__ GemmParams p) {
     using S = PairSmem;
@@ -51,7 +51,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gem
     const uint32_t rank = cluster_ctarank();          // 0 = leader
     const uint32_t pair = blockIdx.x >> 1;
     const uint32_t num_pairs = gridDim.x >> 1;
-    const uint32_t total_tiles = p.m_tiles * p.n_tiles * p.batches;
+    const uint32_t total_tiles = p.m_tiles * p.n_tiles * p.batches * p.split_k;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -82,30 +82,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gem
             const bool is_a = warp == 0;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            const bool mn = (is_a ? p.a_mn_major : p.b_mn_major) != 0;
-            const CUtensorMap* map = is_a ? &p.tm_a : &p.tm_b;
-            const uint32_t* bcast = is_a ? p.a_bcast : p.b_bcast;
-            const uint32_t groups = mn ? (kBlockM * p.elem_bytes) / kRowBytes : 1;   // 128 rows or columns either way
-            const uint32_t mn_group_elems = kRowBytes / p.elem_bytes;
-            const uint32_t mn_group_bytes = p.block_k * kRowBytes;
-            const uint32_t block_k = p.block_k;
+            AFeed a_feed;
+            BFeed<kPairBlockN / 2> b_feed;
+            if (is_a) a_feed.setup(p); else b_feed.setup(p);
             const uint32_t my_bytes = is_a ? uint32_t(S::kABytes) : uint32_t(S::kBBytes);
             const uint32_t dst_off = is_a ? 0u : uint32_t(S::kABytes);
             const uint32_t full0 = mapa_shared(smem_u32(&full_bar[0]), 0);   // the leader's full[0]
             for (uint32_t t = pair; t < total_tiles && ok; t += num_pairs) {
                 const TileCoord tc = decode_tile(p, t);
                 // first row (A) or column (B) this CTA stages
-                const uint32_t mn0 = is_a ? tc.m0 * 2 + rank * kBlockM : tc.n0 * kPairBlockN + rank * (kPairBlockN / 2);
-                uint32_t bi[3];
-                {
-                    uint32_t b = tc.batch;
-                    bi[0] = b % p.bsz[0]; b /= p.bsz[0];
-                    bi[1] = b % p.bsz[1]; b /= p.bsz[1];
-                    bi[2] = b;
-                }
-                const int c2 = bcast[0] ? 0 : bi[0], c3 = bcast[1] ? 0 : bi[1], c4 = bcast[2] ? 0 : bi[2];
-                uint32_t k_elem = 0;
-                for (uint32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+                if (is_a) a_feed.begin_tile(p, tc.m0 * 2 + rank * kBlockM, tc.batch, tc.kb_begin);
+                else b_feed.begin_tile(p, tc.n0 * kPairBlockN + rank * (kPairBlockN / 2), tc.batch, tc.kb_begin);
+                for (uint32_t kb = tc.kb_begin; kb < tc.kb_end; ++kb) {
                     if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, kWaitLimitNs)) {
                         atomicCAS(p.status, 0u, WAIT_PRODUCER_EMPTY);
                         ok = false;
@@ -114,14 +102,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gem
                     uint8_t* dst = smem + stage * S::kStageBytes + dst_off;
                     const uint32_t bar = full0 + stage * 8;
                     if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * my_bytes);   // this CTA's bytes and the partner's
-                    if (!mn) {
-                        tma_load_5d_pair(dst, map, bar, int(k_elem), int(mn0), c2, c3, c4);
-                    } else {
-#pragma unroll
-                        for (uint32_t g = 0; g < 4; ++g)
-                            if (g < groups) tma_load_5d_pair(dst + g * mn_group_bytes, map, bar, int(mn0 + g * mn_group_elems), int(k_elem), c2, c3, c4);
-                    }
-                    k_elem += block_k;
+                    if (is_a) a_feed.load<true>(p, dst, bar);
+                    else b_feed.load<true>(p, dst, bar);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -143,6 +125,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gem
             constexpr uint64_t kStageUnits = S::kStageBytes >> 4;
             const uint32_t idesc = p.idesc;   // M = 256, N = 256
             for (uint32_t t = pair; t < total_tiles && ok; t += num_pairs) {
+                const TileCoord tc = decode_tile(p, t);
                 if (!mbar_wait_bounded(&tmem_empty_bar[acc], acc_phase ^ 1, kWaitLimitNs)) {
                     atomicCAS(p.status, 0u, WAIT_MMA_TMEM_EMPTY);
                     break;
@@ -150,7 +133,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gem
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * kPairBlockN;
                 uint32_t accumulate = 0;
-                for (uint32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+                for (uint32_t kb = tc.kb_begin; kb < tc.kb_end; ++kb) {
                     if (!mbar_wait_bounded(&full_bar[stage], phase, kWaitLimitNs)) {
                         atomicCAS(p.status, 0u, WAIT_MMA_FULL);
                         ok = false;
@@ -192,7 +175,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gem
             }
             tc_fence_after_sync();
             const uint32_t tmem_acc = tmem_base + acc * kPairBlockN + ((sub * 32) << 16);
-            epilogue_tile<kPairBlockN>(p, tc.m0 * 2 + rank * kBlockM, tc.n0 * kPairBlockN, tc.batch, 0, tmem_acc, stage_out, store_buf, sub,
+            epilogue_tile<kPairBlockN>(p, tc.m0 * 2 + rank * kBlockM, tc.n0 * kPairBlockN, tc.batch, tc.split, tmem_acc, stage_out, store_buf, sub,
                                        lane, out_elem);
             tc_fence_before_sync();
             __syncwarp();
