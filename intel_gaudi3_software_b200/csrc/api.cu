@@ -288,10 +288,11 @@ static int launch_gemm_kernel(mmeb200_ctx* c, const GemmParams& p, unsigned grid
 
 // CTA-pair kernel: clusters of two CTAs; the grid is the number of pairs the device can hold at once (a cluster
 // needs both its SMs inside one GPC, so this can be fewer than sm_count / 2), or the tile count if that is smaller.
-template <int KIND>
+template <int KIND, int EPI_GROUPS>
 static int launch_pair_kernel(mmeb200_ctx* c, const GemmParams& p, uint64_t tiles) {
-    auto kern = gemm_tcgen05_pair_kernel<KIND>;
-    constexpr int smem = PairSmem::kTotal;
+    auto kern = gemm_tcgen05_pair_kernel<KIND, EPI_GROUPS>;
+    constexpr int smem = PairSmem<EPI_GROUPS>::kTotal;
+    constexpr int threads = PairSmem<EPI_GROUPS>::kThreads;
     static int max_pairs[16] = {};
     int& cached = max_pairs[c->device & 15];
     if (cached == 0) {
@@ -299,7 +300,7 @@ static int launch_pair_kernel(mmeb200_ctx* c, const GemmParams& p, uint64_t tile
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof cfg);
         cfg.gridDim = dim3(unsigned(c->sm_count) & ~1u);
-        cfg.blockDim = dim3(kGemmThreads);
+        cfg.blockDim = dim3(threads);
         cfg.dynamicSmemBytes = smem;
         cudaLaunchAttribute attr;
         attr.id = cudaLaunchAttributeClusterDimension;
@@ -314,7 +315,7 @@ static int launch_pair_kernel(mmeb200_ctx* c, const GemmParams& p, uint64_t tile
     unsigned pairs = unsigned(std::min<uint64_t>(tiles, uint64_t(cached)));
     if (const char* e = getenv("MME_B200_PAIR_GRID")) pairs = std::max(1, atoi(e));
     if (getenv("MME_B200_DEBUG")) fprintf(stderr, "pair kernel: max active clusters %d, tiles %llu, pairs %u\n", cached, (unsigned long long) tiles, pairs);
-    kern<<<pairs * 2, kGemmThreads, smem, c->stream>>>(p);
+    kern<<<pairs * 2, threads, smem, c->stream>>>(p);
     c->launches++;
     CUDA_OK(c, cudaGetLastError());
     return 0;
@@ -427,9 +428,18 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     int rc;
     if (use_pair) {
         const uint64_t pair_tiles = tiles * split;
-        rc = j.kind == KIND_F16 ? launch_pair_kernel<KIND_F16>(c, p, pair_tiles)
-             : j.kind == KIND_TF32 ? launch_pair_kernel<KIND_TF32>(c, p, pair_tiles)
-                                   : launch_pair_kernel<KIND_F8>(c, p, pair_tiles);
+        // a tile with few k blocks spends longer in its epilogue than in its MMAs: give it eight epilogue warps
+        const uint32_t kb_per_tile = (p.num_k_blocks + split - 1) / split;
+        bool two_groups = kb_per_tile <= 12;
+        if (const char* e = getenv("MME_B200_EPI_GROUPS")) two_groups = atoi(e) == 2;            // tuning knob
+        if (two_groups)
+            rc = j.kind == KIND_F16 ? launch_pair_kernel<KIND_F16, 2>(c, p, pair_tiles)
+                 : j.kind == KIND_TF32 ? launch_pair_kernel<KIND_TF32, 2>(c, p, pair_tiles)
+                                       : launch_pair_kernel<KIND_F8, 2>(c, p, pair_tiles);
+        else
+            rc = j.kind == KIND_F16 ? launch_pair_kernel<KIND_F16, 1>(c, p, pair_tiles)
+                 : j.kind == KIND_TF32 ? launch_pair_kernel<KIND_TF32, 1>(c, p, pair_tiles)
+                                       : launch_pair_kernel<KIND_F8, 1>(c, p, pair_tiles);
     } else if (block_n == 256) {
         rc = j.kind == KIND_F16 ? launch_gemm_kernel<KIND_F16, 256, 4>(c, p, grid)
              : j.kind == KIND_TF32 ? launch_gemm_kernel<KIND_TF32, 256, 4>(c, p, grid)

@@ -21,23 +21,30 @@
 
 namespace mmeb200 {
 
-constexpr int kPairStages = 6;
 constexpr int kPairBlockN = 256;       // columns of the pair's tile; each CTA stages half of them
 
+// EPI_GROUPS = 1: four epilogue warps drain the CTA's 128 x 256 accumulator (six operand stages).
+// EPI_GROUPS = 2: eight epilogue warps, each group of four takes half of the columns (five stages; the
+// second group's output staging buffers take the place of the sixth). For tiles with so few k blocks
+// that the epilogue, not the MMA, sets the pace.
+template <int EPI_GROUPS>
 struct PairSmem {
+    static constexpr int kStages = EPI_GROUPS == 1 ? 6 : 5;
     static constexpr int kABytes = kBlockM * kRowBytes;
     static constexpr int kBBytes = (kPairBlockN / 2) * kRowBytes;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarrierBytes = 1024;
-    static constexpr int kOutStageBytes = 2 * kBlockM * kRowBytes;
-    static constexpr int kTotal = kPairStages * kStageBytes + kBarrierBytes + kOutStageBytes + 1024;
+    static constexpr int kOutStageBytes = EPI_GROUPS * 2 * kBlockM * kRowBytes;
+    static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + kOutStageBytes + 1024;
+    static constexpr int kThreads = 128 + 128 * EPI_GROUPS;
 };
 
 // p.m_tiles counts 256-row tiles here; p.n_tiles counts 256-column tiles.
-template <int KIND>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_pair_kernel(const __grid_constant__ GemmParams p) {
-    using S = PairSmem;
-    constexpr int STAGES = kPairStages;
+template <int KIND, int EPI_GROUPS>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<EPI_GROUPS>::kThreads, 1)
+    gemm_tcgen05_pair_kernel(const __grid_constant__ GemmParams p) {
+    using S = PairSmem<EPI_GROUPS>;
+    constexpr int STAGES = S::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * S::kStageBytes);
@@ -60,7 +67,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gem
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tmem_full_bar[b], 1);
-            mbar_init(&tmem_empty_bar[b], 8);  // four epilogue warps of both CTAs (used in the leader only)
+            mbar_init(&tmem_empty_bar[b], 8 * EPI_GROUPS);  // every epilogue warp of both CTAs (used in the leader only)
         }
         fence_mbar_init();
         tma_prefetch_desc(&p.tm_a);
@@ -159,10 +166,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gem
         __syncwarp();
     } else if (warp >= 4) {
         // ------------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
-        const uint32_t sub = warp & 3;
+        const uint32_t sub = warp & 3;           // tensor-memory lane window of this warp
+        const uint32_t grp = (warp - 4) >> 2;    // which share of the columns
+        constexpr int kGroupCols = kPairBlockN / EPI_GROUPS;
         uint32_t acc = 0, acc_phase = 0;
         const uint32_t out_elem = dtype_size(int(p.out_dtype));
-        uint8_t* stage_out = smem + STAGES * S::kStageBytes + S::kBarrierBytes;
+        uint8_t* stage_out = smem + STAGES * S::kStageBytes + S::kBarrierBytes + grp * (2 * kBlockM * kRowBytes);
         uint32_t store_buf = 0;
         const uint32_t leader_tmem_empty = mapa_shared(smem_u32(&tmem_empty_bar[0]), 0);
         for (uint32_t t = pair; t < total_tiles; t += num_pairs) {
@@ -174,9 +183,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1) gem
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t tmem_acc = tmem_base + acc * kPairBlockN + ((sub * 32) << 16);
-            epilogue_tile<kPairBlockN>(p, tc.m0 * 2 + rank * kBlockM, tc.n0 * kPairBlockN, tc.batch, tc.split, tmem_acc, stage_out, store_buf, sub,
-                                       lane, out_elem);
+            const uint32_t tmem_acc = tmem_base + acc * kPairBlockN + grp * kGroupCols + ((sub * 32) << 16);
+            epilogue_tile<kGroupCols>(p, tc.m0 * 2 + rank * kBlockM, tc.n0 * kPairBlockN + grp * kGroupCols, tc.batch, tc.split, tmem_acc,
+                                      stage_out, store_buf, sub, lane, out_elem);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(leader_tmem_empty + acc * 8);
