@@ -62,12 +62,13 @@ CONV = dict(C=256, K=256, W=56, H=56, B=64, S=3, R=3, pad=1)
 # DRAM bytes per launch of the dominant kernel from an ncu capture (profiles/*.md say which
 # command produced each number); None where no capture exists yet.
 NCU_TRAFFIC_BYTES = {
-    "fp8_gemm_8192": 450.5e6,        # profiles/gemm_tcgen05_fp8_gemm_8192.md
-    "fp8_gemm_8192_bias11": 450.5e6,  # same kernel and byte streams; only the epilogue scale differs
-    "bf16_gemm_8192": 1156.8e6,      # profiles/gemm_tcgen05_other_workloads.md
-    "conv_fwd": 163.7e6,
+    "fp8_gemm_8192": 357.2e6,        # profiles/gemm_tcgen05_pair_fp8_gemm_8192.md
+    "fp8_gemm_8192_bias11": 357.2e6,  # same kernel and byte streams; only the epilogue scale differs
+    "bf16_gemm_8192": 1346.8e6,      # profiles/gemm_tcgen05_pair_other_workloads.md
+    "conv_fwd": 165.8e6,
+    "conv_dedx": 165.5e6,
     "conv_dedw": 210.2e6,
-    "fp8_bgemm_attn": 2154.9e6,
+    "fp8_bgemm_attn": 2155.1e6,
 }
 
 

@@ -370,6 +370,8 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
         p.n_tiles = (j.N + block_n - 1) / block_n;
         units = uint64_t(c->sm_count);
     }
+    p.raster_gm = 16;
+    if (const char* e = getenv("MME_B200_GM")) p.raster_gm = std::max(1, atoi(e));               // tuning knob
     tiles = uint64_t(p.m_tiles) * p.n_tiles * p.batches;
     uint32_t split = 1;
     if (const char* e = getenv("MME_B200_SPLIT_K")) j.force_split = atoi(e);                   // tuning knob
@@ -1663,6 +1665,7 @@ extern "C" int mmeb200_gemm_splitk_static(mmeb200_ctx* c, mmeb200_tensor* out, c
     constexpr int block_n = 128;
     p.n_tiles = uint32_t((N + block_n - 1) / block_n);
     p.split_k = uint32_t(splits);
+    p.raster_gm = 16;
     p.idesc = make_instr_desc(a.hw_fmt, b.hw_fmt, a.mn_major, b.mn_major, kBlockM, block_n);
     p.status = c->d_status;
     p.scale = 1.0f; p.out_dtype = DT_FP32; p.has_cast = 0; p.epi_mode = EPI_F32;

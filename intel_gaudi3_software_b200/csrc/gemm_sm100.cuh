@@ -66,6 +66,7 @@ struct GemmParams {
     uint32_t block_k;       // elements per k block (128 B / element size)
     uint32_t num_k_blocks;  // over the whole K
     uint32_t m_tiles, n_tiles, batches, split_k;
+    uint32_t raster_gm;     // m tiles per raster group: tiles of a group run together and share B panels in L2
     uint32_t bsz[3];
     uint32_t a_bcast[3], b_bcast[3];
     uint32_t a_mn_major, b_mn_major;
@@ -108,7 +109,7 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, uint32_t t
     const uint32_t per_batch = p.m_tiles * p.n_tiles;
     c.batch = t / per_batch;
     const uint32_t r = t % per_batch;
-    constexpr uint32_t GM = 16;
+    const uint32_t GM = p.raster_gm;
     const uint32_t group_span = GM * p.n_tiles;
     const uint32_t first_m = (r / group_span) * GM;
     const uint32_t gsz = min(GM, p.m_tiles - first_m);

@@ -7,7 +7,7 @@
 //   * full[stage] lives in the even-ranked ("leader") CTA. Its two arrivals are the leader's A and B
 //     producer, each announcing the bytes of BOTH CTAs' loads of that operand; the partner's
 //     producers only issue their loads, which complete on the leader's barrier
-//     (cp.async.bulk.tensor ... cta_group::2, no multicast). The partner never makes a remote
+//     (the cta_group::2 form of the tiled load; each CTA fetches its own tile). The partner never makes a remote
 //     arrival per stage: a release-ordered remote arrival costs a round trip between the SMs.
 //   * only the leader's MMA thread issues; its commits arrive on empty[stage] / tmem_full[acc] of
 //     BOTH CTAs (tcgen05.commit ... multicast::cluster).
@@ -63,7 +63,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<EPI_GROUPS>
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full_bar[s], 2);    // the leader's A and B producer (used in the leader only)
-            mbar_init(&empty_bar[s], 1);   // one multicast commit
+            mbar_init(&empty_bar[s], 1);   // one commit, delivered to both CTAs
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tmem_full_bar[b], 1);

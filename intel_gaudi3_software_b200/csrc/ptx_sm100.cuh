@@ -247,7 +247,7 @@ __device__ __forceinline__ bool mbar_wait_bounded_cluster(uint64_t* bar, uint32_
     }
 }
 // Tiled load into this CTA's shared memory whose completion is signalled on `bar_cluster_addr`, which may be the
-// partner's barrier. No multicast: every CTA fetches its own tile.
+// partner's barrier. Every CTA fetches its own tile.
 __device__ __forceinline__ void tma_load_5d_pair(void* dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int c0, int c1, int c2,
                                                  int c3, int c4) {
     asm volatile(
