@@ -355,7 +355,7 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     // Tile geometry. CTA pairs (one 256 x 256 tile per two SMs, half the B traffic per SM) whenever the
     // problem is at least one such tile; else 128 x 256 tiles per CTA whenever N has the columns; else
     // 128 x 128. Split-K below fills the machine when that leaves few tiles.
-    bool use_pair = j.M >= 256 && j.N >= 256 && !c->pending_peer;
+    bool use_pair = j.M >= 256 && j.N >= 256;
     if (const char* e = getenv("MME_B200_PAIR")) use_pair = use_pair && atoi(e) != 0;            // tuning knob
     const bool wide = j.N > 128;
     int block_n = wide ? 256 : 128;
