@@ -61,6 +61,15 @@ def test_implicit_gemm_path(calc, best_oracle, c):
     check_all_ops(calc, best_oracle, c, seed=1)
 
 
+@pytest.mark.parametrize("pair", ["1", "0"])
+def test_implicit_gemm_wide_channels_on_both_kernels(calc, best_oracle, pair, monkeypatch):
+    """256 channels in and out: all three operations qualify for the CTA-pair kernel (pair = 1); pair = 0 forces
+    the single-CTA kernel on the same problem."""
+    monkeypatch.setenv("MME_B200_PAIR", pair)
+    check_all_ops(calc, best_oracle, (256, 256, 20, 18, 2, 3, 3, (1, 1), (1, 1), (1, 1)), seed=3)
+    check_all_ops(calc, best_oracle, (256, 320, 17, 19, 1, 3, 3, (1, 1), (1, 1), (2, 2)), seed=4)
+
+
 def test_implicit_gemm_fp8(calc, best_oracle, port):
     check_all_ops(calc, best_oracle, (128, 128, 32, 32, 2, 3, 3, (1, 1), (1, 1), (1, 1)), dtype=abi.FP8_143, port=port, seed=2, tol=1e-6)
 

@@ -54,6 +54,27 @@ def test_shapes(calc, best_oracle, M, N, K):
     run_case(calc, best_oracle, M, N, K)
 
 
+KERNEL_VARIANTS = {
+    "pair, four epilogue warps": {"MME_B200_PAIR": "1", "MME_B200_EPI_GROUPS": "1"},
+    "pair, eight epilogue warps": {"MME_B200_PAIR": "1", "MME_B200_EPI_GROUPS": "2"},
+    "pair, split-K": {"MME_B200_PAIR": "1", "MME_B200_SPLIT_K": "3"},
+    "single CTA, 256 wide": {"MME_B200_PAIR": "0"},
+    "single CTA, 128 wide": {"MME_B200_BLOCK_N": "128"},
+    "single CTA, no TMA stores": {"MME_B200_PAIR": "0", "MME_B200_NO_TMA_STORE": "1"},
+}
+
+
+@pytest.mark.parametrize("variant", sorted(KERNEL_VARIANTS))
+def test_every_kernel_variant_matches_the_oracle(calc, best_oracle, variant, monkeypatch):
+    """The tile geometry is picked per problem; the tuning knobs force each form on the same problems."""
+    for k, v in KERNEL_VARIANTS[variant].items():
+        monkeypatch.setenv(k, v)   # the library reads its knobs per call
+    run_case(calc, best_oracle, 512, 768, 520, abi.OP_AB, seed=3)
+    run_case(calc, best_oracle, 300, 260, 200, abi.OP_ABT, seed=4)
+    run_case(calc, best_oracle, 256, 256, 96, abi.OP_ATB, batch=(3, 2), w_batch=(1, 2), seed=5)
+    run_case(calc, best_oracle, 384, 520, 72, abi.OP_ATBT, o_pitch=8, seed=6)
+
+
 @pytest.mark.parametrize("op", [abi.OP_AB, abi.OP_ABT, abi.OP_ATB, abi.OP_ATBT])
 def test_operand_orientations(calc, best_oracle, op):
     run_case(calc, best_oracle, 256, 384, 192, op)
