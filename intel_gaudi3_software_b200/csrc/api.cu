@@ -376,8 +376,9 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     uint32_t split = 1;
     if (const char* e = getenv("MME_B200_SPLIT_K")) j.force_split = atoi(e);                   // tuning knob
     if (j.force_split > 0) split = std::min<uint32_t>(j.force_split, p.num_k_blocks);
-    else if (tiles * 2 <= units && p.num_k_blocks >= 8) {
-        split = uint32_t(std::min<uint64_t>(units / tiles, p.num_k_blocks / 4));
+    else if (tiles * 2 <= units && p.num_k_blocks >= 32) {
+        // worth it only when the k loop is long: the partial sums cost a second kernel and (splits + 1) passes over M x N floats
+        split = uint32_t(std::min<uint64_t>(units / tiles, p.num_k_blocks / 8));
         split = std::max(1u, std::min(split, 64u));
     }
     // no empty splits
@@ -481,7 +482,10 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
         r.M = j.M; r.N = j.N; r.batches = p.batches; r.splits = split; r.scale = o.scale; r.cast = o.cast;
         r.rng_philox = o.philox; r.seed = o.seed; r.offset = o.offset;
         const uint64_t total = uint64_t(j.M) * j.N * p.batches;
-        splitk_reduce_kernel<<<grid_for(total, 256, c->sm_count), 256, 0, c->stream>>>(static_cast<const float*>(ws), r);
+        const bool vec4 = j.N % 4 == 0 && o.ld % 4 == 0 && o.bstride[0] % 4 == 0 && o.bstride[1] % 4 == 0 && o.bstride[2] % 4 == 0 &&
+                          (reinterpret_cast<uintptr_t>(o.ptr) & 15) == 0;
+        if (vec4) splitk_reduce_vec4_kernel<<<grid_for(total / 4, 256, c->sm_count), 256, 0, c->stream>>>(static_cast<const float*>(ws), r);
+        else splitk_reduce_kernel<<<grid_for(total, 256, c->sm_count), 256, 0, c->stream>>>(static_cast<const float*>(ws), r);
         c->launches++;
         CUDA_OK(c, cudaGetLastError());
     }

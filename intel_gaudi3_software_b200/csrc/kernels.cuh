@@ -292,6 +292,44 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, ReduceOut r) 
     }
 }
 
+// Four consecutive columns per thread (one 16-byte load per split, one vector store): for outputs whose
+// row length, pitches and base allow it. Same summation order as the scalar kernel, so the same bits.
+__global__ void splitk_reduce_vec4_kernel(const float* __restrict__ ws, ReduceOut r) {
+    const uint64_t per = uint64_t(r.M) * r.N;
+    const uint64_t total = per * r.batches;
+    const uint64_t total4 = total / 4;
+    const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
+    const int elem = dtype_size(int(r.out_dtype));
+    for (uint64_t q = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; q < total4; q += stride) {
+        float4 s = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (uint32_t k = 0; k < r.splits; ++k) {
+            const float4 v = __ldcs(reinterpret_cast<const float4*>(ws + uint64_t(k) * total) + q);   // read once: do not keep in L2
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        const uint64_t i = q * 4;
+        uint32_t bits[4] = {__float_as_uint(s.x * r.scale), __float_as_uint(s.y * r.scale), __float_as_uint(s.z * r.scale),
+                            __float_as_uint(s.w * r.scale)};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (f32_is_nan(bits[j])) bits[j] = kF32CanonNan;
+            if (r.has_cast) {
+                if (r.cast.relu) bits[j] = relu_bits(bits[j]);
+                bits[j] = cast_from_f32(bits[j], r.cast, r.rng_philox ? philox_word(r.seed, r.offset, i + j) : 0u);
+            }
+        }
+        uint64_t b = i / per;
+        const uint64_t rem = i % per;
+        const uint64_t row = rem / r.N, col = rem % r.N;
+        const uint64_t b0 = b % r.bsz[0]; b /= r.bsz[0];
+        const uint64_t b1 = b % r.bsz[1]; b /= r.bsz[1];
+        const uint64_t o = b0 * r.out_bstride[0] + b1 * r.out_bstride[1] + b * r.out_bstride[2] + row * r.out_ld + col;
+        uint8_t* dst = static_cast<uint8_t*>(r.out) + o * elem;
+        if (elem == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(bits[0], bits[1], bits[2], bits[3]);
+        else if (elem == 2) *reinterpret_cast<uint2*>(dst) = make_uint2((bits[0] & 0xFFFFu) | (bits[1] << 16), (bits[2] & 0xFFFFu) | (bits[3] << 16));
+        else *reinterpret_cast<uint32_t*>(dst) = (bits[0] & 0xFFu) | ((bits[1] & 0xFFu) << 8) | ((bits[2] & 0xFFu) << 16) | (bits[3] << 24);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // dedw across GPUs, fused with the split-K reduction: every rank sums its K-splits (ascending)
 // and stores the result straight into slot [rank] of EVERY rank's slot buffer over NVLink (plain
