@@ -383,6 +383,19 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     }
     // no empty splits
     while (split > 1 && ((p.num_k_blocks + split - 1) / split) * (split - 1) >= p.num_k_blocks) --split;
+    // A small problem that is not split and would leave most SMs idle runs as 128 x 128 tiles: half the work per SM
+    // on up to four times as many SMs (1024^3 bf16: 11.5 us instead of 14.4 us).
+    if (split == 1 && !getenv("MME_B200_BLOCK_N") && !getenv("MME_B200_PAIR")) {
+        const uint64_t sms_used = use_pair ? tiles * 2 : tiles;
+        const uint64_t t128 = uint64_t((j.M + 127) / 128) * ((j.N + 127) / 128) * p.batches;
+        if (sms_used * 2 <= uint64_t(c->sm_count) && t128 <= uint64_t(c->sm_count) && t128 > sms_used) {
+            use_pair = false;
+            block_n = 128;
+            p.m_tiles = (j.M + kBlockM - 1) / kBlockM;
+            p.n_tiles = (j.N + 127) / 128;
+            tiles = t128;
+        }
+    }
     p.split_k = split;
     p.idesc = use_pair ? make_instr_desc(j.a.hw_fmt, j.b.hw_fmt, j.a.mn_major, j.b.mn_major, 256, 256)
                        : make_instr_desc(j.a.hw_fmt, j.b.hw_fmt, j.a.mn_major, j.b.mn_major, kBlockM, block_n);
