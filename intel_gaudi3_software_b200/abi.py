@@ -65,6 +65,15 @@ class CompareResult(C.Structure):
     _fields_ = [("mismatches", C.c_uint64), ("first_index", C.c_uint64)]
 
 
+class GenerateParams(C.Structure):
+    """mmeb200_generate_params."""
+    _fields_ = [("kind", C.c_int32), ("min_value", C.c_float), ("max_value", C.c_float), ("mean", C.c_float), ("std_dev", C.c_float),
+                ("packing", C.c_uint32), ("level", C.c_uint32), ("seed", C.c_uint64)]
+
+
+GEN_UNIFORM, GEN_NORMAL, GEN_FILL, GEN_UNIT, GEN_REDUCTION_PACKING = 0, 1, 2, 3, 4
+
+
 def dense_strides(sizes):
     s, acc = [], 1
     for n in sizes:
@@ -157,6 +166,7 @@ SYMBOLS = {
     "mmeb200_launch_count": (C.c_uint64, [C.c_void_p]),
     "mmeb200_version": (C.c_char_p, []),
     "mmeb200_compare": (C.c_int, [C.c_void_p, P(Tensor), P(Tensor), C.c_uint, C.c_uint, C.c_int, P(CompareResult)]),
+    "mmeb200_generate": (C.c_int, [C.c_void_p, P(Tensor), P(GenerateParams)]),
     "mmeb200_peer_alloc": (C.c_int, [C.c_void_p, C.c_size_t, P(C.c_void_p), C.c_char_p]),
     "mmeb200_peer_open": (C.c_int, [C.c_void_p, C.c_char_p, P(C.c_void_p)]),
     "mmeb200_peer_close": (C.c_int, [C.c_void_p, C.c_void_p]),

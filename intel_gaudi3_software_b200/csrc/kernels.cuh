@@ -499,6 +499,50 @@ __global__ void strided_copy_kernel(void* __restrict__ out, const void* __restri
     }
 }
 
+// RandomSimTensorGenerator on the device (mme/mme_reference/sim_tensor.cpp:100-191): uniform in [lo, hi], normal(mean, std)
+// clamped to [lo, hi], constant fill, "unit matrix" (first element hi, the rest lo, :131-137) and the 0/1 packing
+// pattern of reductionAdd (:157-183); lo / hi arrive already clamped to the output type's finite range. Values are
+// rounded to the output type with round-to-nearest-even, as the typed constructors do (:274-297). The random stream is
+// Philox keyed by (seed, element index), not the reference's mt19937 sequence.
+struct GenerateParams {
+    void* out;
+    uint64_t n;
+    int kind;            // 0 uniform, 1 normal, 2 fill, 3 unit matrix, 4 reduction packing
+    float lo, hi, mean, std_dev;
+    uint64_t seed;
+    uint32_t packing, row_size;
+    int out_dtype;
+    CastSpec cast;
+};
+__global__ void generate_kernel(GenerateParams g) {
+    const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
+    const int elem = dtype_size(g.out_dtype);
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < g.n; i += stride) {
+        float v;
+        if (g.kind == 0) {
+            const float u = float(philox_word(g.seed, 0, i) >> 8) * (1.0f / 16777216.0f);   // [0, 1)
+            v = fminf(g.lo + u * (g.hi - g.lo), g.hi);
+        } else if (g.kind == 1) {
+            // Box-Muller on two independent words (u1 in (0, 1], u2 in [0, 1))
+            const float u1 = (float(philox_word(g.seed, 0, i) >> 8) + 1.0f) * (1.0f / 16777216.0f);
+            const float u2 = float(philox_word(g.seed ^ 0x9E3779B97F4A7C15ull, 0, i) >> 8) * (1.0f / 16777216.0f);
+            const float z = sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
+            v = fminf(fmaxf(g.mean + g.std_dev * z, g.lo), g.hi);
+        } else if (g.kind == 2) {
+            v = g.lo;
+        } else if (g.kind == 3) {
+            v = i == 0 ? g.hi : g.lo;
+        } else {
+            const uint64_t row = i / g.row_size, col = i % g.row_size;
+            v = (row == col % g.packing) ? 1.0f : 0.0f;
+        }
+        uint32_t bits = __float_as_uint(v);
+        if (g.out_dtype == DT_TF32) bits = tf32_rne(bits);
+        else if (g.out_dtype != DT_FP32) bits = cast_from_f32(bits, g.cast, 0u);
+        store_cast(g.out, i, bits, elem);
+    }
+}
+
 // TensorComparator::doCompare on the device: `a` holds num_partials stacked results (summed in fp32,
 // in order, then rounded to the element type) and `b` the tensor to compare with; counts mismatching
 // elements and finds the lowest mismatching index. bit_exact compares raw bits instead.
