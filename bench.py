@@ -278,7 +278,7 @@ def run_ours(args):
         exchange = None
         if wl.get("fused_exchange"):
             from intel_gaudi3_software_b200.multi_gpu import PeerExchange
-            exchange = PeerExchange(calc, int(np.prod(oshape)), dist, rank, world)
+            exchange = PeerExchange(calc, int(np.prod(oshape)), dist, rank, world, deferred_output=True)
         elif wl["op"] == abi.OP_DEDW and dist is not None:
             # dW partials are all-reduced over NCCL on a second stream, double-buffered, so that the
             # exchange of step i overlaps the convolution of step i+1 (as it would overlap the next

@@ -298,7 +298,9 @@ typedef struct mmeb200_peer_group {
     void* slots[MMEB200_MAX_PEERS];      /* slots[j]: rank j's slot buffer (world * n fp32), addressable from this GPU */
     uint32_t* flags[MMEB200_MAX_PEERS];  /* flags[j]: rank j's arrival counter (zero before the first exchange) */
     uint32_t step;                       /* exchanges already done on this (slots, flags) set */
-    uint32_t reserved;
+    uint32_t deferred_output;            /* non-zero (device `out` only): the final wait-and-add runs on a side stream and
+                                            overlaps the next call's convolution; `out` is complete after the next
+                                            mmeb200_sync, and is ordered before the next exchange's output */
 } mmeb200_peer_group;
 /* cudaMalloc'd, zero-filled device memory plus the handle other processes open it with. */
 int mmeb200_peer_alloc(mmeb200_ctx* ctx, size_t bytes, void** dev_ptr, unsigned char handle[MMEB200_PEER_HANDLE_BYTES]);

@@ -57,7 +57,7 @@ class CastParams(C.Structure):
 class PeerGroup(C.Structure):
     """mmeb200_peer_group: slot buffers and arrival flags of the ranks taking part in a fused dedw exchange."""
     _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("slots", C.c_void_p * 8), ("flags", C.c_void_p * 8),
-                ("step", C.c_uint32), ("reserved", C.c_uint32)]
+                ("step", C.c_uint32), ("deferred_output", C.c_uint32)]
 
 
 class CompareResult(C.Structure):

@@ -44,6 +44,10 @@ struct mmeb200_ctx {
     const mmeb200_peer_group* pending_peer = nullptr;   // set by mmeb200_conv_dedw_allreduce for the next GEMM
     cudaStream_t s_h2d = nullptr, s_d2h = nullptr;   // copy streams of the pipelined host-tensor GEMM
     cudaEvent_t ev_in[17] = {}, ev_done[17] = {};
+    // deferred output of the fused dedw exchange: the wait-and-add kernel runs here
+    cudaStream_t s_side = nullptr;
+    cudaEvent_t ev_scatter = nullptr, ev_gather = nullptr;
+    bool gather_pending = false;
     uint64_t launches = 0;
 
     int fail(int code, const char* fmt, ...) {
@@ -170,6 +174,10 @@ static int stage_out(mmeb200_ctx* c, Staged* s) {
 }
 
 static int collect_status(mmeb200_ctx* c) {
+    if (c->gather_pending) {   // a deferred exchange output: everything after this point is ordered behind it
+        CUDA_OK(c, cudaStreamWaitEvent(c->stream, c->ev_gather, 0));
+        c->gather_pending = false;
+    }
     CUDA_OK(c, cudaMemcpyAsync(c->h_status, c->d_status, 4, cudaMemcpyDeviceToHost, c->stream));
     CUDA_OK(c, cudaStreamSynchronize(c->stream));
     if (*c->h_status != 0) {
@@ -474,6 +482,15 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
         ps.block_counter = c->d_status + 8;
         ps.rank = peer->rank; ps.world = peer->world; ps.splits = split; ps.n = n; ps.scale = o.scale;
         const unsigned blocks = grid_for(n / 4, 256, c->sm_count);
+        const bool deferred = peer->deferred_output != 0;
+        if (deferred && !c->s_side) {
+            CUDA_OK(c, cudaStreamCreateWithFlags(&c->s_side, cudaStreamNonBlocking));
+            CUDA_OK(c, cudaEventCreateWithFlags(&c->ev_scatter, cudaEventDisableTiming));
+            CUDA_OK(c, cudaEventCreateWithFlags(&c->ev_gather, cudaEventDisableTiming));
+        }
+        // A rank may announce step i+1 only after it has read its slots of step i: the partners' next-but-one stores
+        // reuse them, and they are held back only by this rank's arrivals.
+        if (c->gather_pending) CUDA_OK(c, cudaStreamWaitEvent(c->stream, c->ev_gather, 0));
         splitk_reduce_peer_scatter_kernel<<<blocks, 256, 0, c->stream>>>(static_cast<const float*>(ws), ps);
         PeerGather pg;
         memset(&pg, 0, sizeof pg);
@@ -482,7 +499,16 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
         pg.target = uint32_t(peer->world) * (peer->step + 1);
         pg.world = peer->world; pg.n = n; pg.out = static_cast<float*>(o.ptr); pg.status = c->d_status;
         pg.limit_ns = 1000000000ull;
-        peer_gather_sum_kernel<<<blocks, 256, 0, c->stream>>>(pg);
+        if (deferred) {
+            CUDA_OK(c, cudaEventRecord(c->ev_scatter, c->stream));
+            CUDA_OK(c, cudaStreamWaitEvent(c->s_side, c->ev_scatter, 0));
+            peer_gather_sum_kernel<<<blocks, 256, 0, c->s_side>>>(pg);
+            CUDA_OK(c, cudaEventRecord(c->ev_gather, c->s_side));
+            c->gather_pending = true;
+        } else {
+            peer_gather_sum_kernel<<<blocks, 256, 0, c->stream>>>(pg);
+            c->gather_pending = false;
+        }
         c->launches += 2;
         CUDA_OK(c, cudaGetLastError());
         return 0;
@@ -894,6 +920,12 @@ void mmeb200_destroy(mmeb200_ctx* c) {
     if (!c) return;
     cudaSetDevice(c->device);
     cudaStreamSynchronize(c->stream);
+    if (c->s_side) {
+        cudaStreamSynchronize(c->s_side);
+        cudaStreamDestroy(c->s_side);
+        cudaEventDestroy(c->ev_scatter);
+        cudaEventDestroy(c->ev_gather);
+    }
     for (auto& b : c->arena) cudaFree(b.ptr);
     if (c->d_status) cudaFree(c->d_status);
     if (c->h_status) cudaFreeHost(c->h_status);
@@ -983,6 +1015,10 @@ int mmeb200_timer_start(mmeb200_ctx* c) {
 }
 int mmeb200_timer_stop(mmeb200_ctx* c, float* ms) {
     if (!c || !ms) return MMEB200_ERR_INVALID_ARG;
+    if (c->gather_pending) {   // a deferred exchange output belongs to the timed work
+        CUDA_OK(c, cudaStreamWaitEvent(c->stream, c->ev_gather, 0));
+        c->gather_pending = false;
+    }
     CUDA_OK(c, cudaEventRecord(c->ev1, c->stream));
     CUDA_OK(c, cudaEventSynchronize(c->ev1));
     CUDA_OK(c, cudaEventElapsedTime(ms, c->ev0, c->ev1));
@@ -1498,7 +1534,9 @@ int mmeb200_conv_dedw_allreduce(mmeb200_ctx* c, mmeb200_tensor* out, const mmeb2
     for (int i = 0; i < g->world; ++i)
         if (!g->slots[i] || !g->flags[i]) return c->fail(MMEB200_ERR_INVALID_ARG, "peer group: rank %d has no slot buffer or flag", i);
     if (out->dtype != DT_FP32 || !is_dense(out)) return c->fail(MMEB200_ERR_INVALID_ARG, "the summed dW must be a dense fp32 tensor");
-    c->pending_peer = g;
+    mmeb200_peer_group group = *g;
+    if (out->mem_space != MMEB200_MEM_DEVICE) group.deferred_output = 0;   // a host output is copied back before the call returns
+    c->pending_peer = &group;
     const int rc = mmeb200_conv(c, out, x, w, y, params, MMEB200_OP_DEDW, RM_NE, nullptr);
     c->pending_peer = nullptr;
     return rc;

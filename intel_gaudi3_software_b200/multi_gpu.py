@@ -87,9 +87,12 @@ class PeerExchange:
     `dedw_allreduce` alternates between the two sets, which is what lets ranks drift apart by one step.
     """
 
-    def __init__(self, calc, n_floats, dist=None, rank=0, world=1):
+    def __init__(self, calc, n_floats, dist=None, rank=0, world=1, deferred_output=False):
+        """deferred_output: with a device-resident `out`, the final wait-and-add of an exchange overlaps the next call's
+        convolution; `out` is then complete after the calculator's next sync()."""
         assert 1 <= world <= 8
         self.calc, self.rank, self.world, self.n = calc, rank, world, n_floats
+        self.deferred_output = deferred_output
         self.calls = 0
         mine = []
         for _ in range(2):
@@ -106,6 +109,7 @@ class PeerExchange:
         for b in range(2):
             g = abi.PeerGroup()
             g.rank, g.world, g.step = rank, world, 0
+            g.deferred_output = int(deferred_output)
             for j in range(world):
                 if j == rank:
                     g.slots[j], g.flags[j] = mine[b][0], mine[b][2]

@@ -50,6 +50,23 @@ def main():
         ok &= bool((lo == hi).all().item())
     dist.barrier()
     ex.close()
+    # device-resident tensors with the deferred output: the final add of step i overlaps the convolution of step i+1
+    ex2 = PeerExchange(calc, n, dist, rank, world, deferred_output=True)
+    dx, dw, dy, dout = calc.to_device(xr), calc.to_device(wb), calc.to_device(yr), calc.alloc(n * 4)
+    dev = abi.MEM_DEVICE
+    for it in range(7):
+        ex2.dedw_allreduce(T(dout.ptr, abi.FP32, ws, mem_space=dev), T(dx.ptr, abi.BF16, xs_r, mem_space=dev),
+                           T(dw.ptr, abi.BF16, ws, mem_space=dev), T(dy.ptr, abi.BF16, ys_r, mem_space=dev), cp)
+    calc.sync(10_000_000_000)
+    out = dout.download(np.float32)
+    ok &= bool(np.abs(out - full).max() <= 2e-5 * np.abs(full).max())
+    t = torch.from_numpy(out.view(np.int32).copy()).cuda()
+    lo, hi = t.clone(), t.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    ok &= bool((lo == hi).all().item())
+    dist.barrier()
+    ex2.close()
     calc.close()
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)

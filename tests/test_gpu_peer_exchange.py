@@ -46,6 +46,26 @@ def test_world_of_one_matches_plain_dedw(calc):
     ex.close()
 
 
+def test_world_of_one_deferred_output_on_device_tensors(calc):
+    """Device tensors with the deferred output: the final add runs on a side stream and is joined by sync()."""
+    xb, wb, yb = inputs(2)
+    cp = abi.make_conv_params(2, (1, 1), (1, 1), (1, 1))
+    n = int(np.prod(CASE["ws"]))
+    plain = np.zeros(n, np.float32)
+    calc.do_convolution(T(plain, abi.FP32, CASE["ws"]), T(xb, abi.BF16, CASE["xs"]), T(wb, abi.BF16, CASE["ws"]), T(yb, abi.BF16, CASE["ys"]), cp, abi.OP_DEDW)
+    ex = PeerExchange(calc, n, deferred_output=True)
+    dx, dw, dy, dout = calc.to_device(xb), calc.to_device(wb), calc.to_device(yb), calc.alloc(n * 4)
+    dev = abi.MEM_DEVICE
+    for it in range(5):
+        ex.dedw_allreduce(T(dout.ptr, abi.FP32, CASE["ws"], mem_space=dev), T(dx.ptr, abi.BF16, CASE["xs"], mem_space=dev),
+                          T(dw.ptr, abi.BF16, CASE["ws"], mem_space=dev), T(dy.ptr, abi.BF16, CASE["ys"], mem_space=dev), cp)
+    calc.sync(10_000_000_000)
+    assert (dout.download(np.float32).view(np.uint32) == plain.view(np.uint32)).all()
+    ex.close()
+    for b in (dx, dw, dy, dout):
+        b.free()
+
+
 def test_unsatisfiable_wait_ends_by_itself():
     c = pkg.Calculator(device=0)
     xb, wb, yb = inputs(1)
