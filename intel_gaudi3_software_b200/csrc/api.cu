@@ -320,9 +320,7 @@ static int launch_pair_kernel(mmeb200_ctx* c, const GemmParams& p, uint64_t tile
         if (n <= 0) return c->fail(MMEB200_ERR_CUDA, "no CTA pair fits on this device");
         cached = n;
     }
-    unsigned pairs = unsigned(std::min<uint64_t>(tiles, uint64_t(cached)));
-    if (const char* e = getenv("MME_B200_PAIR_GRID")) pairs = std::max(1, atoi(e));
-    if (getenv("MME_B200_DEBUG")) fprintf(stderr, "pair kernel: max active clusters %d, tiles %llu, pairs %u\n", cached, (unsigned long long) tiles, pairs);
+    const unsigned pairs = unsigned(std::min<uint64_t>(tiles, uint64_t(cached)));
     kern<<<pairs * 2, threads, smem, c->stream>>>(p);
     c->launches++;
     CUDA_OK(c, cudaGetLastError());
