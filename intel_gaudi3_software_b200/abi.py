@@ -71,6 +71,7 @@ class GenerateParams(C.Structure):
                 ("packing", C.c_uint32), ("level", C.c_uint32), ("seed", C.c_uint64)]
 
 
+ACC_TENSOR_CORE, ACC_CHIP_EXACT = 0, 1
 GEN_UNIFORM, GEN_NORMAL, GEN_FILL, GEN_UNIT, GEN_REDUCTION_PACKING = 0, 1, 2, 3, 4
 
 
@@ -166,6 +167,7 @@ SYMBOLS = {
     "mmeb200_launch_count": (C.c_uint64, [C.c_void_p]),
     "mmeb200_version": (C.c_char_p, []),
     "mmeb200_compare": (C.c_int, [C.c_void_p, P(Tensor), P(Tensor), C.c_uint, C.c_uint, C.c_int, P(CompareResult)]),
+    "mmeb200_set_accumulation": (C.c_int, [C.c_void_p, C.c_int]),
     "mmeb200_generate": (C.c_int, [C.c_void_p, P(Tensor), P(GenerateParams)]),
     "mmeb200_peer_alloc": (C.c_int, [C.c_void_p, C.c_size_t, P(C.c_void_p), C.c_char_p]),
     "mmeb200_peer_open": (C.c_int, [C.c_void_p, C.c_char_p, P(C.c_void_p)]),

@@ -107,6 +107,10 @@ class Calculator:
         self._check(self.lib.mmeb200_compare(self.ctx, a, b, cd_size, num_partials, int(bit_exact), C.byref(r)))
         return int(r.mismatches), int(r.first_index)
 
+    def set_accumulation(self, mode):
+        """abi.ACC_TENSOR_CORE (default) or abi.ACC_CHIP_EXACT (accumulators bit-identical to the reference's Gaudi3 model)."""
+        self._check(self.lib.mmeb200_set_accumulation(self.ctx, mode))
+
     def generate(self, out, kind, min_value=0.0, max_value=0.0, mean=0.0, std_dev=0.0, seed=0, packing=0, level=0):
         """RandomSimTensorGenerator on the device: fills `out` (uniform / normal / fill / unit / reduction packing)."""
         g = abi.GenerateParams(kind, min_value, max_value, mean, std_dev, packing, level, seed)

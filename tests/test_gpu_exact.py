@@ -1,0 +1,123 @@
+"""The bit-exact accumulation mode (mmeb200_set_accumulation(MMEB200_ACC_CHIP_EXACT)): accumulators, and everything
+downstream of them, must equal the reference's Gaudi3 model bit for bit -- GEMM in every orientation, fp8 with every
+bias / Inf-NaN convention (random codes, so Inf and NaN occur), the rounded cast including the LFSR stochastic stream,
+and the three convolutions."""
+import numpy as np
+import pytest
+
+import intel_gaudi3_software_b200 as pkg
+from intel_gaudi3_software_b200 import abi
+from intel_gaudi3_software_b200.abi import make_tensor as T
+import util
+from golden.make_golden import conv_shapes
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def exact():
+    c = pkg.Calculator(device=0)
+    c.set_accumulation(abi.ACC_CHIP_EXACT)
+    yield c
+    c.close()
+
+
+def bits(a):
+    return a.view(np.uint32)
+
+
+@pytest.mark.parametrize("op", [abi.OP_AB, abi.OP_ABT, abi.OP_ATB, abi.OP_ATBT])
+def test_bf16_gemm_bit_exact(exact, best_oracle, op):
+    rng = np.random.default_rng(op)
+    for (M, N, K, batch, xb_dims, wb_dims) in ((70, 129, 203, (), None, None), (64, 64, 8, (3, 2), (3, 1), (1, 2)), (5, 3, 1, (), None, None),
+                                               (200, 96, 1000, (2,), None, None)):
+        tA, tB = op in (abi.OP_ATB, abi.OP_ATBT), op in (abi.OP_ABT, abi.OP_ATBT)
+        xbd = list(batch if xb_dims is None else xb_dims)
+        wbd = list(batch if wb_dims is None else wb_dims)
+        xs = ([M, K] if tA else [K, M]) + xbd
+        ws = ([K, N] if tB else [N, K]) + wbd
+        os_ = [N, M] + list(batch)
+        # wide exponent spread: alignment and truncation matter
+        xb = util.gen_bf16(rng, int(np.prod(xs)), "normal") ^ (rng.integers(0, 2, int(np.prod(xs))).astype(np.uint16) << 9)
+        wb = util.gen_bf16(rng, int(np.prod(ws)), "normal", 50.0)
+        o1, o2 = np.full(int(np.prod(os_)), 7.0, np.float32), np.full(int(np.prod(os_)), 7.0, np.float32)
+        exact.do_batch_gemm(T(o1, abi.FP32, os_), T(xb, abi.BF16, xs), T(wb, abi.BF16, ws), op)
+        assert best_oracle.bgemm(T(o2, abi.FP32, os_), T(xb, abi.BF16, xs), T(wb, abi.BF16, ws), op) == 0
+        assert (bits(o1) == bits(o2)).all(), (op, M, N, K, int((bits(o1) != bits(o2)).sum()))
+
+
+@pytest.mark.parametrize("tx,tw,bx,bw,mx,mw", [(9, 9, 7, 7, 2, 2), (9, 9, 3, 15, 2, 0), (10, 9, 15, 11, 0, 2), (10, 10, 20, 1, 1, 0), (9, 10, 15, 30, 1, 2)])
+def test_fp8_gemm_bit_exact_on_random_codes(exact, best_oracle, tx, tw, bx, bw, mx, mw):
+    rng = np.random.default_rng(tx * 31 + bw)
+    M, N, K = 96, 80, 333
+    xb, wb = rng.integers(0, 256, M * K).astype(np.uint8), rng.integers(0, 256, K * N).astype(np.uint8)
+    x, w = T(xb, tx, [K, M], fp_bias=bx, inf_nan_mode=mx), T(wb, tw, [N, K], fp_bias=bw, inf_nan_mode=mw)
+    o1, o2 = np.zeros(M * N, np.float32), np.zeros(M * N, np.float32)
+    exact.do_batch_gemm(T(o1, abi.FP32, [N, M]), x, w, abi.OP_AB)
+    assert best_oracle.bgemm(T(o2, abi.FP32, [N, M]), x, w, abi.OP_AB) == 0
+    assert (bits(o1) == bits(o2)).all(), int((bits(o1) != bits(o2)).sum())
+    if mx == 2 and mw == 2:
+        assert np.isnan(o2).any()        # the NaN codes took the general routine
+    # finite codes only: the fast routine alone
+    xb2, wb2 = xb & 0x77, wb & 0x77
+    x2, w2 = T(xb2, tx, [K, M], fp_bias=bx, inf_nan_mode=mx), T(wb2, tw, [N, K], fp_bias=bw, inf_nan_mode=mw)
+    exact.do_batch_gemm(T(o1, abi.FP32, [N, M]), x2, w2, abi.OP_AB)
+    assert best_oracle.bgemm(T(o2, abi.FP32, [N, M]), x2, w2, abi.OP_AB) == 0
+    assert np.isfinite(o2).all() and (bits(o1) == bits(o2)).all()
+
+
+def test_cast_after_exact_accumulation_is_bit_exact_including_stochastic_rounding(exact, port, best_oracle):
+    rng = np.random.default_rng(8)
+    M, N, K = 130, 70, 96
+    xb, wb = util.gen_bf16(rng, M * K, "normal"), util.gen_bf16(rng, K * N, "normal")
+    x, w = T(xb, abi.BF16, [K, M]), T(wb, abi.BF16, [N, K])
+    acc = np.zeros(M * N, np.float32)
+    assert best_oracle.bgemm(T(acc, abi.FP32, [N, M]), x, w, abi.OP_AB) == 0
+    regs = np.arange(5, 261, dtype=np.uint32)
+    for od, bias, mode, rm in ((abi.BF16, 0, 0, abi.RM_NE), (abi.BF16, 0, 0, abi.RM_SR), (abi.FP8_143, 7, 2, abi.RM_SR), (abi.FP8_152, 15, 0, abi.RM_NE)):
+        cp = abi.make_cast_params(rm, clip_fp=True)
+        want = np.zeros(M * N, abi.NP_DTYPE[od])
+        rc, _ = port.activation(T(want, od, [N, M], fp_bias=bias, inf_nan_mode=mode), T(acc.copy(), abi.FP32, [N, M]), cp, regs.copy(), 41)
+        assert rc == 0
+        got = np.zeros(M * N, abi.NP_DTYPE[od])
+        exact.set_lfsr(regs, 41)
+        exact.do_batch_gemm(T(got, od, [N, M], fp_bias=bias, inf_nan_mode=mode), x, w, abi.OP_AB, cp)
+        assert (got == want).all(), (od, rm, int((got != want).sum()))
+
+
+@pytest.mark.parametrize("c", [
+    (16, 24, 12, 10, 2, 3, 3, (1, 1), (1, 1), (1, 1)),
+    (64, 64, 20, 18, 2, 3, 3, (1, 1), (1, 1), (1, 1)),      # a geometry the tensor-core mode would run through im2col-mode TMA
+    (24, 16, 15, 11, 2, 5, 3, (2, 1), (2, 1), (1, 2)),
+    (8, 8, 8, 8, 1, 1, 1, (2, 2), (0, 0), (1, 1)),
+])
+def test_convolutions_bit_exact(exact, best_oracle, c):
+    rng = np.random.default_rng(c[0] + c[5])
+    xs, ws, ys = conv_shapes(c)
+    xb = util.gen_bf16(rng, int(np.prod(xs)), "normal")
+    wb = util.gen_bf16(rng, int(np.prod(ws)), "normal", 0.05)
+    yb = util.gen_bf16(rng, int(np.prod(ys)), "normal", 0.01)
+    x, w, y = T(xb, abi.BF16, xs), T(wb, abi.BF16, ws), T(yb, abi.BF16, ys)
+    cp = abi.make_conv_params(2, c[8], c[7], c[9])
+    for op, shp in ((abi.OP_FWD, ys), (abi.OP_DEDX, xs), (abi.OP_DEDW, ws)):
+        o1, o2 = np.full(int(np.prod(shp)), 3.0, np.float32), np.full(int(np.prod(shp)), 3.0, np.float32)
+        exact.do_convolution(T(o1, abi.FP32, shp), x, w, y, cp, op)
+        assert best_oracle.conv(T(o2, abi.FP32, shp), x, w, y, cp, op) == 0
+        assert (bits(o1) == bits(o2)).all(), (op, c, int((bits(o1) != bits(o2)).sum()))
+
+
+def test_mode_rules(calc):
+    c2 = pkg.Calculator(chip=abi.CHIP_GAUDI2)
+    with pytest.raises(Exception, match="Gaudi3"):
+        c2.set_accumulation(abi.ACC_CHIP_EXACT)
+    c2.close()
+    c3 = pkg.Calculator()
+    c3.set_accumulation(abi.ACC_CHIP_EXACT)
+    a = np.ones(64, np.float32)
+    o = np.zeros(64, np.float32)
+    with pytest.raises(Exception, match="bf16 x bf16 or fp8 x fp8"):
+        c3.do_batch_gemm(T(o, abi.FP32, [8, 8]), T(a, abi.FP32, [8, 8]), T(a, abi.FP32, [8, 8]), abi.OP_AB)
+    c3.set_accumulation(abi.ACC_TENSOR_CORE)
+    c3.do_batch_gemm(T(o, abi.FP32, [8, 8]), T(a, abi.FP32, [8, 8]), T(a, abi.FP32, [8, 8]), abi.OP_AB)
+    assert (o == 8.0).all()
+    c3.close()
