@@ -50,7 +50,7 @@ class DeviceBuffer:
 class Calculator:
     """CPUCalculator(chip, ..., seed, lfsrNumRegs, lfsr, polynomial) on one B200."""
 
-    def __init__(self, chip=abi.CHIP_GAUDI3, device=0, seed=0, lfsr_num_regs=256, lfsr=None, polynomial=0):
+    def __init__(self, chip=abi.CHIP_GAUDI3, device=0, seed=0, lfsr_num_regs=256, lfsr=None, polynomial=0, accumulation=abi.ACC_TENSOR_CORE):
         self.lib = abi.load_library()
         ctx = C.c_void_p()
         regs = None
@@ -63,6 +63,8 @@ class Calculator:
             raise MmeError(rc, "mmeb200_create failed (no B200 visible?)" if rc == abi.ERR_NO_DEVICE else "mmeb200_create failed")
         self.ctx = ctx
         self.device = device
+        if accumulation != abi.ACC_TENSOR_CORE:
+            self.set_accumulation(accumulation)
 
     def close(self):
         if getattr(self, "ctx", None):

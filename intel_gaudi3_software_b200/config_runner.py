@@ -16,7 +16,7 @@ distribution the config asks for (uniform in [min, max], clamped normal, or a co
 mme_test_data_gen.cpp:553-600,783-817), limits clamped to the operand type's finite range and values rounded to
 the type with round-to-nearest-even, as the reference does (sim_tensor.cpp:116-119,274-297).
 
-    python -m intel_gaudi3_software_b200.config_runner my_tests.json [--seed 7] [--dump out_dir]
+    python -m intel_gaudi3_software_b200.config_runner my_tests.json [--seed 7] [--dump out_dir] [--exact]
 """
 import argparse
 import itertools
@@ -435,10 +435,13 @@ def main(argv=None):
     ap.add_argument("--repeats", type=int, default=1)
     ap.add_argument("--device", type=int, default=0)
     ap.add_argument("--dump", help="directory that receives each test's output tensor as raw bytes")
+    ap.add_argument("--exact", action="store_true", help="accumulate with the reference's Gaudi3 arithmetic (bit-identical results; bf16 / fp8 operands)")
     args = ap.parse_args(argv)
     from .calculator import Calculator
     tests = Parser(args.seed).parse_file(args.config, args.repeats)
     calc = Calculator(device=args.device, seed=args.seed)
+    if args.exact:
+        calc.set_accumulation(abi.ACC_CHIP_EXACT)
     if args.dump:
         os.makedirs(args.dump, exist_ok=True)
     failed = 0

@@ -81,6 +81,31 @@ def test_config_cases_match_the_oracle(calc, best_oracle):
     assert not failures, failures[:10]
 
 
+def test_config_cases_are_bit_identical_in_exact_mode(best_oracle):
+    """With the bit-exact accumulation mode every case on bf16 / fp8 operands must reproduce the oracle's output bytes:
+    accumulation, masked second GEMM, cast (stochastic rounding included) and the reduction into memory."""
+    import intel_gaudi3_software_b200 as pkg
+    calc = pkg.Calculator(device=0)
+    calc.set_accumulation(abi.ACC_CHIP_EXACT)
+    tests = cr.Parser(SEED).parse_file(CASES)
+    lfsr, poly = calc.get_lfsr(256)
+    checked, failures = 0, []
+    narrow = (abi.BF16, abi.FP8_143, abi.FP8_152)
+    for i, t in enumerate(tests):
+        if t["operation"] in cr.DMA_OPS or t["inTypeFloat"] not in narrow or t["in2TypeFloat"] not in narrow:
+            continue
+        if (t["inTypeFloat"] == abi.BF16) != (t["in2TypeFloat"] == abi.BF16):
+            continue
+        calc.set_lfsr(lfsr, poly)
+        got, tt = cr.run_test(calc, t)
+        want = oracle_flow(best_oracle, t, tt, lfsr, poly)
+        checked += 1
+        if not (got.view(np.uint8) == want.view(np.uint8)).all():
+            failures.append((i, t["testName"], cr.OP_NAMES[t["operation"]], int((got != want).sum())))
+    calc.close()
+    assert checked >= 70 and not failures, (checked, failures[:10])
+
+
 def test_command_line(tmp_path):
     env = dict(os.environ, PYTHONPATH=os.path.dirname(HERE))
     p = subprocess.run([sys.executable, "-m", "intel_gaudi3_software_b200.config_runner", CASES, "--seed", str(SEED), "--dump", str(tmp_path)],
