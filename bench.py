@@ -50,6 +50,9 @@ WORKLOADS = {
                            w_dtype=abi.FP8_143, bias=7, out_dtype=abi.BF16, bound="hbm", peak_scale=2.0, dtype="fp8_143"),
     "fp8_mlp": dict(kind="gemm", M=16384, N=28672, K=8192, in_dtype=abi.FP8_152, w_dtype=abi.FP8_143, bias=7,
                     out_dtype=abi.BF16, bound="tensor", peak_scale=2.0, dtype="fp8_152xfp8_143"),
+    # the optional bit-exact Gaudi3 accumulation (integer emulation on the CUDA cores; no tensor cores)
+    "fp8_gemm_2048_exact": dict(kind="gemm", M=2048, N=2048, K=2048, in_dtype=abi.FP8_143, w_dtype=abi.FP8_143, bias=7,
+                                out_dtype=abi.FP32, bound="tensor", peak_scale=2.0, dtype="fp8_143", exact=True),
     "conv_fwd": dict(kind="conv", op=abi.OP_FWD, out_dtype=abi.BF16, bound="tensor", peak_scale=1.0, dtype="bf16"),
     "conv_dedx": dict(kind="conv", op=abi.OP_DEDX, out_dtype=abi.BF16, bound="tensor", peak_scale=1.0, dtype="bf16"),
     "conv_dedw": dict(kind="conv", op=abi.OP_DEDW, out_dtype=abi.FP32, bound="tensor", peak_scale=1.0, dtype="bf16"),
@@ -233,6 +236,8 @@ def run_ours(args):
     wl = WORKLOADS[args.workload]
     rank, world, local, dist = dist_setup(args.gpus)
     calc = pkg.Calculator(device=local)
+    if wl.get("exact"):
+        calc.set_accumulation(abi.ACC_CHIP_EXACT)
     lib, ctx = calc.lib, calc.ctx
     flops, alg_bytes = workload_counts(wl)
     cast = abi.make_cast_params(abi.RM_NE) if wl["out_dtype"] != abi.FP32 else None
@@ -399,7 +404,8 @@ def run_ours(args):
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
         "config": {"workload": args.workload, "per_gpu": {k: v for k, v in wl.items() if k in ("M", "N", "K", "batch")} or CONV,
-                   "accumulate": "fp32", "output": "bf16 RNE" if wl["out_dtype"] == abi.BF16 else "fp32",
+                   "accumulate": "Gaudi3 tree, bit-exact (integer emulation, no tensor cores: the tensor peak is shown for scale only)" if wl.get("exact") else "fp32",
+                   "output": "bf16 RNE" if wl["out_dtype"] == abi.BF16 else "fp32",
                    "l2": "operands + output (%d MiB) exceed the 126 MB L2; no flush between steps" % ((in_bytes + out_bytes) >> 20)
                    if in_bytes + out_bytes > L2_BYTES else "working set fits L2 (latency-bound correctness config)",
                    "sharding": "rows of A / images per rank, replica of B / weights" if wl.get("op") != abi.OP_DEDW else
