@@ -64,6 +64,7 @@ enum {
     MMEB200_OP_ABT = 6,
     MMEB200_OP_ATB = 7,
     MMEB200_OP_ATBT = 8,
+    MMEB200_OP_GEMM_TRANSPOSE = 9, /* the calculator treats it as TRANS (mme_reference_impl.cpp:430-443) */
     MMEB200_OP_MEMCPY = 10,
     MMEB200_OP_TRANS = 11
 };
@@ -209,7 +210,7 @@ int mmeb200_convert(mmeb200_ctx* ctx, mmeb200_tensor* out, const mmeb200_tensor*
                     const mmeb200_cast_params* cast);
 
 /* Replaces CPUCalculator::doDma (mme_reference_impl.cpp:396-443): MEMCPY or TRANS (swap of the
- * two fastest dims). */
+ * two fastest dims); GEMM_TRANSPOSE is the same transposition. */
 int mmeb200_dma(mmeb200_ctx* ctx, mmeb200_tensor* out, const mmeb200_tensor* x, int op);
 
 /* Read / overwrite the LFSR registers and polynomial (m_lfsr, m_polynomial,

@@ -37,10 +37,10 @@ TYPE_NAMES = {"bf16": abi.BF16, "fp32": abi.FP32, "fp32_non_ieee": abi.FP32, "fp
 UNSUPPORTED_TYPES = ("fp16", "ufp16")
 OPERATIONS = {"fwd": abi.OP_FWD, "dedx": abi.OP_DEDX, "transposed_dedx": abi.OP_TRANSPOSED_DEDX, "dedw": abi.OP_DEDW,
               "ab": abi.OP_AB, "abt": abi.OP_ABT, "atb": abi.OP_ATB, "atbt": abi.OP_ATBT, "memcpy": abi.OP_MEMCPY,
-              "transpose": abi.OP_TRANS}
+              "transpose": abi.OP_TRANS, "gemm_transpose": abi.OP_GEMM_TRANSPOSE, "reductionAdd": abi.OP_REDUCTION_ADD}
 CONV_OPS = (abi.OP_FWD, abi.OP_DEDX, abi.OP_TRANSPOSED_DEDX, abi.OP_DEDW)
 GEMM_OPS = (abi.OP_AB, abi.OP_ABT, abi.OP_ATB, abi.OP_ATBT)
-DMA_OPS = (abi.OP_MEMCPY, abi.OP_TRANS)
+DMA_OPS = (abi.OP_MEMCPY, abi.OP_TRANS, abi.OP_GEMM_TRANSPOSE)
 ROUNDING = {"rn": 0, "rz": 1, "ru": 2, "rd": 3, "rs": 4, "rhaz": 6, "rsn": 7}
 REDUCTION_OPS = {"add": 0, "sub": 1, "min": 2, "max": 3, "max_0": 4, "none": 5}
 REDUCTION_RM = {"rn": 0, "rz": 1, "ru": 2, "rd": 3}
@@ -68,7 +68,7 @@ def default_test():
          "padding": [0, 0, 0], "dilation": [1, 1, 1], "strides": [1, 1, 1],
          "xMean": 0.0, "wMean": 0.0, "yMean": 0.0, "xStd": 0.0, "wStd": 0.0, "yStd": 0.0,
          "xMinVal": -1.0, "wMinVal": -1.0, "yMinVal": -1.0, "xMaxVal": 10.0, "wMaxVal": 10.0, "yMaxVal": 10.0,
-         "ignored": []}
+         "packingFactor": 1, "reductionLevel": 1, "ignored": []}
     for k in BOOL_KEYS:
         t[k] = False
     return t
@@ -187,6 +187,8 @@ class Parser:
                 t[key] = bool(self.rng.integers(0, 2)) if value == "random" else _to_bool(value)
             elif key in NUM_KEYS:
                 t[key] = _number(value)
+            elif key in ("packingFactor", "reductionLevel"):
+                t[key] = int(_number(value))
             elif key in ("dilation", "strides", "padding"):
                 lo, hi = (0, 2) if key == "padding" else (1, 3)
                 t[key] = [int(self.rng.integers(lo, hi + 1)) if v == "random" else int(_number(v)) for v in value]
@@ -319,6 +321,8 @@ def common_dim_size(t):
     """Length of the reduction, which sets the comparator's allowance (mme_test_manager.cpp: getCDSize use)."""
     op, x, w, y = t["operation"], t["xSizes"], t["wSizes"], t["ySizes"]
     filt = int(np.prod(w[2:]))
+    if op == abi.OP_REDUCTION_ADD:
+        return t["packingFactor"] * t["reductionLevel"]
     if op in (abi.OP_AB, abi.OP_ABT):
         return x[0]
     if op in (abi.OP_ATB, abi.OP_ATBT):
@@ -351,6 +355,13 @@ class TestTensors:
                 self.host[role] = self._generate(calc, role, n, seed + k, constant=v)
             elif role == "w" and t["operation"] in DMA_OPS:
                 continue
+            elif role == "x" and t["operation"] == abi.OP_REDUCTION_ADD:
+                # the packing operand: 1 where row == column % packing (mme_test_data_gen.cpp:603-615, sim_tensor.cpp:157-183)
+                dtype, bias, mode = self.attr["x"]
+                out = np.zeros(n, abi.NP_DTYPE[dtype])
+                calc.generate(T(out, dtype, [n], fp_bias=bias, inf_nan_mode=mode), abi.GEN_REDUCTION_PACKING, 0.0, 1.0,
+                              packing=t["packingFactor"], level=t["reductionLevel"])
+                self.host[role] = out
             else:
                 self.host[role] = self._generate(calc, role, n, seed + k)
         if t["maskedBgemm"]:
@@ -409,6 +420,16 @@ def run_test(calc, t, tensors=None):
         if op in CONV_OPS:
             params = abi.make_conv_params(3, t["padding"], t["strides"], t["dilation"], relu=False)
             calc.do_convolution(acc_t, tt.tensor("x"), tt.tensor("w"), tt.tensor("y"), params, op, abi.RM_NE)
+        elif op == abi.OP_REDUCTION_ADD:
+            # sums `level` partial results with one GEMM against the packing operand: w and the output are viewed as 2-D
+            # (mme_test_manager.cpp:838-853)
+            p_, l_ = t["packingFactor"], t["reductionLevel"]
+            if n_out % p_ or tt.host["w"].size != n_out * l_ or tt.host["x"].size != p_ * p_ * l_:
+                raise ConfigError("reductionAdd: sizes do not fit packingFactor %d and reductionLevel %d" % (p_, l_))
+            wd, wb, wm = tt.attr["w"]
+            xd, xb, xm = tt.attr["x"]
+            calc.do_batch_gemm(T(acc, abi.FP32, [n_out // p_, p_]), T(tt.host["x"], xd, [l_ * p_, p_], fp_bias=xb, inf_nan_mode=xm),
+                               T(tt.host["w"], wd, [n_out // p_, l_ * p_], fp_bias=wb, inf_nan_mode=wm), abi.OP_AB)
         else:
             calc.do_batch_gemm(acc_t, tt.tensor("x"), tt.tensor("w"), op)
         if t["maskedBgemm"]:

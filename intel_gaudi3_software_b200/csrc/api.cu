@@ -1724,6 +1724,7 @@ int mmeb200_dma(mmeb200_ctx* c, mmeb200_tensor* out, const mmeb200_tensor* x, in
     cudaSetDevice(c->device);
     TRY(check_tensor(c, out, "output"));
     TRY(check_tensor(c, x, "x"));
+    if (op == MMEB200_OP_GEMM_TRANSPOSE) op = MMEB200_OP_TRANS;   // same transposition in the calculator
     if (op != MMEB200_OP_MEMCPY && op != MMEB200_OP_TRANS) return c->fail(MMEB200_ERR_INVALID_ARG, "invalid operation");
     if (dtype_size(out->dtype) != dtype_size(x->dtype)) return c->fail(MMEB200_ERR_INVALID_ARG, "element sizes differ");
     const bool tr = op == MMEB200_OP_TRANS;

@@ -9,7 +9,7 @@ import intel_gaudi3_software_b200 as pkg
 from intel_gaudi3_software_b200 import abi
 from intel_gaudi3_software_b200.abi import make_tensor as T
 import util
-from golden.make_golden import conv_shapes
+from golden.make_golden import CONV_CASES, GEMM_CASES, conv_shapes
 
 pytestmark = pytest.mark.gpu
 
@@ -123,6 +123,42 @@ def test_convolutions_bit_exact(exact, best_oracle, c):
         exact.do_convolution(T(o1, abi.FP32, shp), x, w, y, cp, op)
         assert best_oracle.conv(T(o2, abi.FP32, shp), x, w, y, cp, op) == 0
         assert (bits(o1) == bits(o2)).all(), (op, c, int((bits(o1) != bits(o2)).sum()))
+
+
+def test_committed_golden_outputs_are_reproduced_bit_for_bit(exact, golden):
+    """tests/golden/golden_small.npz holds outputs of the compiled reference (Gaudi3 model: chip 2); no oracle is needed here."""
+    for i, (M, N, K, op, batch) in enumerate(GEMM_CASES):
+        tA, tB = op in (abi.OP_ATB, abi.OP_ATBT), op in (abi.OP_ABT, abi.OP_ATBT)
+        xs = ([M, K] if tA else [K, M]) + list(batch)
+        ws = ([K, N] if tB else [N, K]) + list(batch)
+        want = golden["gemm%d_chip2" % i]
+        o = np.zeros(want.size, np.float32)
+        exact.do_batch_gemm(T(o, abi.FP32, [N, M] + list(batch)), T(golden["gemm%d_x" % i], abi.BF16, xs), T(golden["gemm%d_w" % i], abi.BF16, ws), op)
+        assert (bits(o) == bits(np.ascontiguousarray(want, np.float32))).all(), ("gemm", i)
+    M, N, K = 16, 24, 40
+    for j, (tx, tw, bx, bw, mx, mw) in enumerate(((9, 9, 7, 11, 2, 2), (10, 9, 15, 7, 0, 2), (9, 10, 3, 20, 1, 1), (9, 9, 15, 15, 0, 0))):
+        o = np.zeros(M * N, np.float32)
+        exact.do_batch_gemm(T(o, abi.FP32, [N, M]), T(golden["fp8gemm_x"], tx, [K, M], fp_bias=bx, inf_nan_mode=mx),
+                            T(golden["fp8gemm_w"], tw, [N, K], fp_bias=bw, inf_nan_mode=mw), abi.OP_AB)
+        assert (bits(o) == golden["fp8gemm_%d" % j]).all(), ("fp8", j)
+    for dt, nm in ((abi.FP32, "fp32"), (abi.TF32, "tf32")):
+        o = np.zeros(M * N, np.float32)
+        exact.do_batch_gemm(T(o, abi.FP32, [N, M]), T(golden["f32gemm_x"], dt, [K, M]), T(golden["f32gemm_w"], dt, [N, K]), abi.OP_AB)
+        assert (bits(o) == bits(np.ascontiguousarray(golden["f32gemm_" + nm], np.float32))).all(), nm
+    for i, c in enumerate(CONV_CASES):
+        xs, ws, ys = conv_shapes(c)
+        cp = abi.make_conv_params(2, c[8], c[7], c[9])
+        if i == 0:
+            o = np.zeros(int(np.prod(xs)), np.float32)
+            exact.do_convolution(T(o, abi.FP32, xs), T(golden["conv0_x"], abi.BF16, xs), T(golden["tdedx_w"], abi.BF16, [ws[1], ws[0], ws[2], ws[3]]),
+                                 T(golden["conv0_y"], abi.BF16, ys), cp, abi.OP_TRANSPOSED_DEDX)
+            assert (bits(o) == bits(np.ascontiguousarray(golden["tdedx_out"], np.float32))).all(), "transposed_dedx"
+        x, w, y = T(golden["conv%d_x" % i], abi.BF16, xs), T(golden["conv%d_w" % i], abi.BF16, ws), T(golden["conv%d_y" % i], abi.BF16, ys)
+        for op, nm, shp in ((abi.OP_FWD, "fwd", ys), (abi.OP_DEDX, "dedx", xs), (abi.OP_DEDW, "dedw", ws)):
+            want = np.ascontiguousarray(golden["conv%d_%s" % (i, nm)], np.float32)
+            o = np.full(want.size, 3.0, np.float32)
+            exact.do_convolution(T(o, abi.FP32, shp), x, w, y, cp, op)
+            assert (bits(o) == bits(want)).all(), ("conv", i, nm)
 
 
 def test_mode_rules(calc):
