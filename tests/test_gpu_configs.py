@@ -215,3 +215,88 @@ def test_full_size_properties_fp8_gemm(calc):
     assert (d2.download(np.float32) == Port().fp8_to_fp32(xb, 4, 7, 2)).all()
     for buf in (dx, dw, d1, d2, dxp, de):
         buf.free()
+
+
+def _exact_calculator():
+    import intel_gaudi3_software_b200 as pkg
+    c = pkg.Calculator(device=0)
+    c.set_accumulation(abi.ACC_CHIP_EXACT)
+    return c
+
+
+def test_config2_every_output_against_the_exact_mode(calc):
+    """Config 2 at full size, all 67 M outputs: the tensor-core accumulators against the bit-exact Gaudi3 mode (itself pinned to
+    the reference on the smaller cases and the committed golden outputs), within 1e-5 * sum|a_k b_k| per element; and the bf16
+    outputs of the two under the reference's own comparator rule, on the device."""
+    wl = bench.WORKLOADS["fp8_gemm_8192"]
+    n = 8192
+    xb, wb = bench.synth_inputs(wl, seed=2)
+    kw = dict(fp_bias=7, inf_nan_mode=abi.INFNAN_MINIMAL, mem_space=1)
+    ex = _exact_calculator()
+    dx, dw = calc.to_device(xb), calc.to_device(wb)
+    d_fast, d_exact, d_abs = calc.alloc(n * n * 4), calc.alloc(n * n * 4), calc.alloc(n * n * 4)
+    x, w = T(dx.ptr, abi.FP8_143, [n, n], **kw), T(dw.ptr, abi.FP8_143, [n, n], **kw)
+    calc.do_batch_gemm(T(d_fast.ptr, abi.FP32, [n, n], mem_space=1), x, w, abi.OP_AB)
+    calc.sync(20_000_000_000)
+    ex.do_batch_gemm(T(d_exact.ptr, abi.FP32, [n, n], mem_space=1), x, w, abi.OP_AB)
+    ex.sync(60_000_000_000)
+    # sum|a||b| with the sign bits cleared, on the tensor cores (exact enough for a bound)
+    dxa, dwa = calc.to_device(xb & 0x7F), calc.to_device(wb & 0x7F)
+    calc.do_batch_gemm(T(d_abs.ptr, abi.FP32, [n, n], mem_space=1), T(dxa.ptr, abi.FP8_143, [n, n], **kw), T(dwa.ptr, abi.FP8_143, [n, n], **kw), abi.OP_AB)
+    calc.sync(20_000_000_000)
+    fast, exact, sabs = d_fast.download(np.float32), d_exact.download(np.float32), d_abs.download(np.float32)
+    worst = 0.0
+    for lo in range(0, n * n, 1 << 24):   # in slabs, to keep host memory modest
+        hi = lo + (1 << 24)
+        d = np.abs(fast[lo:hi].astype(np.float64) - exact[lo:hi])
+        worst = max(worst, float((d / np.maximum(sabs[lo:hi], 1e-30)).max()))
+    assert worst <= util.ACC_TOL, worst
+    # bf16 outputs: fused cast on the tensor-core path against exact accumulators cast separately
+    o_fast, o_exact = calc.alloc(n * n * 2), calc.alloc(n * n * 2)
+    cp = abi.make_cast_params(abi.RM_NE)
+    calc.do_batch_gemm(T(o_fast.ptr, abi.BF16, [n, n], mem_space=1), x, w, abi.OP_AB, cp)
+    calc.sync(20_000_000_000)
+    ex.do_activation(T(o_exact.ptr, abi.BF16, [n * n], mem_space=1), T(d_exact.ptr, abi.FP32, [n * n], mem_space=1), cp)
+    ex.sync(20_000_000_000)
+    bad, first = calc.compare(T(o_fast.ptr, abi.BF16, [n * n], mem_space=1), T(o_exact.ptr, abi.BF16, [n * n], mem_space=1), n)
+    # The comparator allows 10 % (or 4 ulp): only outputs where the products cancel almost completely can differ by more while
+    # the accumulators agree to 1e-5 * sum|ab| -- a handful in 67 M, each with |acc| far below sum|ab|.
+    assert bad <= n * n // 1_000_000, (bad, first)
+    if bad:
+        assert abs(float(exact[first])) <= 1e-4 * float(sabs[first]), (first, float(exact[first]), float(sabs[first]))
+    for b in (dx, dw, dxa, dwa, d_fast, d_exact, d_abs, o_fast, o_exact):
+        b.free()
+    ex.close()
+
+
+@pytest.mark.parametrize("opname", ["conv_fwd", "conv_dedx", "conv_dedw"])
+def test_config3_4_every_output_against_the_exact_mode(calc, opname):
+    """Configs 3 and 4 at full size: implicit-GEMM convolutions on the tensor cores against the bit-exact mode (im2col + exact GEMM
+    + col2im, the reference's own lowering), all outputs, norm-wise tolerance as in the sliced oracle checks."""
+    wl = bench.WORKLOADS[opname]
+    xs, ws, ys = bench.conv_shapes()
+    xb, wb, yb = bench.synth_inputs(wl, seed=3)
+    cp = abi.make_conv_params(2, (1, 1), (1, 1), (1, 1))
+    op = wl["op"]
+    oshape = {abi.OP_FWD: ys, abi.OP_DEDX: xs, abi.OP_DEDW: ws}[op]
+    n_out = int(np.prod(oshape))
+    ex = _exact_calculator()
+    dx, dw, dy = calc.to_device(xb), calc.to_device(wb), calc.to_device(yb)
+    d_fast, d_exact = calc.alloc(n_out * 4), calc.alloc(n_out * 4)
+    tens = (T(dx.ptr, abi.BF16, xs, mem_space=1), T(dw.ptr, abi.BF16, ws, mem_space=1), T(dy.ptr, abi.BF16, ys, mem_space=1))
+    calc.do_convolution(T(d_fast.ptr, abi.FP32, oshape, mem_space=1), *tens, cp, op)
+    calc.sync(20_000_000_000)
+    ex.do_convolution(T(d_exact.ptr, abi.FP32, oshape, mem_space=1), *tens, cp, op)
+    ex.sync(120_000_000_000)
+    fast, exact = d_fast.download(np.float32), d_exact.download(np.float32)
+    assert np.isfinite(exact).all() and np.abs(exact).max() > 0
+    if op == abi.OP_DEDW:
+        # 200704-term sums: the chip truncates after every block of eight, which biases its sums toward zero by up to
+        # ~25088 half-ulps; the bound is the accumulator tolerance with sum|ab| ~ 200704 * E|x| * E|dy| = 200704 * 0.8 * 0.008
+        tol = util.ACC_TOL * 200704 * 0.8 * 0.008
+    else:
+        tol = 2e-5 * np.abs(exact).max()
+    assert np.abs(fast - exact).max() <= tol, (opname, float(np.abs(fast - exact).max()), float(np.abs(exact).max()))
+    for b in (dx, dw, dy, d_fast, d_exact):
+        b.free()
+    ex.close()
