@@ -71,3 +71,38 @@ def test_bit_exact_and_errors(calc):
         calc.compare(T(a, abi.BF16, [1000]), T(a.astype(np.uint32), abi.FP32, [1000]), 1)
     with pytest.raises(Exception, match="sizes do not match"):
         calc.compare(T(a, abi.BF16, [1000]), T(b[:10].copy(), abi.BF16, [10]), 1)
+
+
+def _sum_1_to_45(calc, dtype):
+    """1 + 2 + ... + 45 accumulated in the tensor's own arithmetic (round to nearest even), as the reference's tests do with
+    bfloat16::add / float addition (mme/tests/unit_tests/mme_unit_test.cpp:238-290): 45 read-modify-write adds on the GPU."""
+    acc = np.zeros(1, abi.NP_DTYPE[dtype])
+    for count in range(1, 46):
+        term = np.zeros(1, abi.NP_DTYPE[dtype])
+        calc.generate(T(term, dtype, [1]), abi.GEN_FILL, float(count), float(count))
+        calc.do_memory_write(T(acc, dtype, [1]), T(term, dtype, [1]), abi.RED_ADD, 0)
+    return acc[0]
+
+
+@pytest.mark.parametrize("dtype", [abi.FP32, abi.BF16])
+def test_fill_and_compare_cases_of_the_reference(calc, dtype):
+    """fill_and_compare_float / _bfloat16 and comparison_failure_bf16 of the reference's unit tests (:238-392), on the device:
+    a tensor filled with 1035 equals one holding 1 + ... + 45 accumulated in the tensor's type; adding 100 from element 1000
+    on is reported, with the first differing element at offset 1000."""
+    sizes = [64, 32, 32, 64]
+    n = int(np.prod(sizes))
+    filled = np.zeros(n, abi.NP_DTYPE[dtype])
+    calc.generate(T(filled, dtype, sizes), abi.GEN_FILL, 1035.0, 1035.0)
+    total = _sum_1_to_45(calc, dtype)
+    accumulated = np.full(n, total, abi.NP_DTYPE[dtype])
+    if dtype == abi.FP32:
+        assert total == 1035.0
+    assert calc.compare(T(filled, dtype, sizes), T(accumulated, dtype, sizes), 0)[0] == 0
+    bumped = np.array([total], abi.NP_DTYPE[dtype])
+    hundred = np.zeros(1, abi.NP_DTYPE[dtype])
+    calc.generate(T(hundred, dtype, [1]), abi.GEN_FILL, 100.0, 100.0)
+    calc.do_memory_write(T(bumped, dtype, [1]), T(hundred, dtype, [1]), abi.RED_ADD, 0)
+    accumulated[1000:] = bumped[0]
+    bad, first = calc.compare(T(filled, dtype, sizes), T(accumulated, dtype, sizes), 0)
+    assert bad == n - 1000 and first == 1000
+    assert first % sizes[0] + (first // sizes[0] % sizes[1]) * sizes[0] == 1000   # the reference's own check of the offset
