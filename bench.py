@@ -486,7 +486,7 @@ def cpu_run(lib, wl, rows, threads, seed=1000):
 
 def pick_rows(lib, wl, threads, budget_s):
     """Calibrate on a tiny sample, then size the bounded sample to about budget_s of CPU work."""
-    probe = max(2, min(threads, 8)) if wl["kind"] == "gemm" else 2
+    probe = max(2, threads) if wl["kind"] == "gemm" else 2   # one row per thread: the probe sees the parallel rate
     dt, fl = cpu_run(lib, wl, probe, threads)
     per_row = dt / probe
     rows = int(max(probe, min(budget_s / max(per_row, 1e-6), 4096 if wl["kind"] == "gemm" else CONV["H"])))

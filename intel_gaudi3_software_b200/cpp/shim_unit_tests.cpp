@@ -7,6 +7,8 @@
 
 #include "mme_reference.h"
 #include "data_types/non_standard_dtypes.h"
+#include "sim_tensor.h"
+#include "tensor_comparator.h"
 
 using namespace MmeCommon;
 
@@ -163,6 +165,54 @@ static void unsupported_type_asserts()
     EXPECT(threw);  // MME_ASSERT -> MMEStackException, never a silent CPU result
 }
 
+// fill_and_compare_float / fill_and_compare_bfloat16 / comparison_failure_bf16 (mme_unit_test.cpp:238-392) with the drop-in
+// TensorComparator: the reference's generator and typed arithmetic build the tensors, the comparison runs on the GPU.
+static void fill_and_compare()
+{
+    SizeArray sizes = {64, 32, 32, 64, 1};
+    RandomSimTensorGenerator generator(1);
+    {
+        pMMESimTensor filled = std::make_shared<MmeSimTensor>(sizes, 4, e_type_fp32), acc = std::make_shared<MmeSimTensor>(sizes, 4, e_type_fp32);
+        generator.fill(filled, 1035);
+        float v = 0;
+        for (unsigned count = 1; count < 46; count++) v += (float) count;
+        for (unsigned e = 0; e < acc->getSizeInElements(); e++) ((float*) acc->data())[e] = v;
+        TensorComparator comparator(false, e_type_fp32);
+        EXPECT(comparator.doCompare(filled, "fillTensor", acc, "accumulatedTensor"));
+        EXPECT(comparator.doCompareBitExact(filled, "fillTensor", acc, "accumulatedTensor"));
+        EXPECT(!comparator.getDiffElement().is_set());
+    }
+    {
+        pMMESimTensor filled = std::make_shared<MmeSimTensor>(sizes, 4, e_type_bf16), acc = std::make_shared<MmeSimTensor>(sizes, 4, e_type_bf16);
+        generator.fill(filled, 1035);
+        bf16_t v(0.0f);
+        for (unsigned count = 1; count < 46; count++) v = bfloat16::add(v, bf16_t((float) count));
+        for (unsigned e = 0; e < acc->getSizeInElements(); e++) ((bf16_t*) acc->data())[e] = v;
+        TensorComparator comparator(false, e_type_bf16);
+        EXPECT(comparator.doCompare(filled, "fillTensor", acc, "accumulatedTensor"));
+        // from element 1000 on the values are 100 higher: reported, with the first difference at offset 1000
+        const bf16_t bumped = bfloat16::add(v, bf16_t(100.0f));
+        for (unsigned e = 1000; e < acc->getSizeInElements(); e++) ((bf16_t*) acc->data())[e] = bumped;
+        EXPECT(!comparator.doCompare(filled, "fillTensor", acc, "accumulatedTensor", 0, "", 1, false));
+        Settable<SizeArray> d = comparator.getDiffElement();
+        EXPECT(d.is_set());
+        if (d.is_set())
+        {
+            EXPECT(d.value()[0] + d.value()[1] * sizes[0] == 1000);
+            EXPECT(d.value()[2] == 0 && d.value()[3] == 0 && d.value()[4] == 0);
+        }
+    }
+    {
+        Matrix a(e_type_fp32, 3, 4), b(e_type_fp32, 3, 4);
+        for (unsigned e = 0; e < 12; e++) { ((float*) a.data())[e] = float(e); ((float*) b.data())[e] = float(e); }
+        TensorComparator comparator(16, e_type_fp32);
+        EXPECT(comparator.doCompare(a, "a", b, "b"));
+        ((float*) b.data())[7] = 1000.0f;
+        EXPECT(!comparator.doCompareBitExact(a, "a", b, "b"));
+        EXPECT(comparator.getDiffElement().is_set() && comparator.getDiffElement().value()[0] == 1 && comparator.getDiffElement().value()[1] == 3);
+    }
+}
+
 int main()
 {
     gemm_simple_fp32();
@@ -176,6 +226,7 @@ int main()
     conv_fwd_fp8<fp8_152_t>(e_type_fp8_152, EXPONENT_BIAS_FP8_152_15);
     gemm_api_bf16_transposed();
     unsupported_type_asserts();
+    fill_and_compare();
     std::printf(g_failures ? "shim unit tests: %d FAILED\n" : "shim unit tests: all passed\n", g_failures);
     return g_failures ? 1 : 0;
 }
