@@ -60,6 +60,15 @@ WORKLOADS = {
     "conv_dedw_fused": dict(kind="conv", op=abi.OP_DEDW, out_dtype=abi.FP32, bound="tensor", peak_scale=1.0, dtype="bf16",
                             fused_exchange=True),
 }
+# HBM-bound helper kernels of the path (cast, comparator, memory-write reduction, tensor generator): one pass over n elements.
+# value = algorithmic GB/s (bytes each kernel must read and write once); they run on tensors far larger than L2.
+STREAM_WORKLOADS = {
+    "cast_f32_to_bf16": dict(kind="stream", n=1 << 28, bytes_per_elem=6, dtype="f32"),          # doActivation, RNE
+    "compare_bf16": dict(kind="stream", n=1 << 29, bytes_per_elem=4, dtype="bf16"),             # TensorComparator rule
+    "memory_write_add_f32": dict(kind="stream", n=1 << 28, bytes_per_elem=12, dtype="f32"),     # doMemoryWrite add: 2 reads + 1 write
+    "generate_uniform_bf16": dict(kind="stream", n=1 << 29, bytes_per_elem=2, dtype="bf16"),    # RandomSimTensorGenerator
+}
+WORKLOADS.update(STREAM_WORKLOADS)
 CONV = dict(C=256, K=256, W=56, H=56, B=64, S=3, R=3, pad=1)
 
 # DRAM bytes per launch of the dominant kernel from an ncu capture (profiles/*.md say which
@@ -231,9 +240,70 @@ def barrier_and_max(dist, value, local):
     return float(t.item())
 
 
+def run_stream(args):
+    """One of the HBM-bound helper kernels on device-resident tensors (single GPU)."""
+    import intel_gaudi3_software_b200 as pkg
+    wl = WORKLOADS[args.workload]
+    calc = pkg.Calculator(device=0)
+    n = wl["n"]
+    dev = abi.MEM_DEVICE
+    bufs = []
+
+    def alloc(nbytes):
+        b = calc.alloc(nbytes)
+        bufs.append(b)
+        return b
+    if args.workload == "cast_f32_to_bf16":
+        src, dst = alloc(n * 4), alloc(n * 2)
+        calc.generate(T(src.ptr, abi.FP32, [n], mem_space=dev), abi.GEN_NORMAL, -100.0, 100.0, 0.0, 1.0, seed=1)
+        cp = abi.make_cast_params(abi.RM_NE)
+        step = lambda: calc.do_activation(T(dst.ptr, abi.BF16, [n], mem_space=dev), T(src.ptr, abi.FP32, [n], mem_space=dev), cp)  # noqa: E731
+    elif args.workload == "compare_bf16":
+        a, b = alloc(n * 2), alloc(n * 2)
+        for buf, seed in ((a, 1), (b, 1)):
+            calc.generate(T(buf.ptr, abi.BF16, [n], mem_space=dev), abi.GEN_UNIFORM, -4.0, 4.0, seed=seed)
+        step = lambda: calc.compare(T(a.ptr, abi.BF16, [n], mem_space=dev), T(b.ptr, abi.BF16, [n], mem_space=dev), 4096)  # noqa: E731
+    elif args.workload == "memory_write_add_f32":
+        mem, src = alloc(n * 4), alloc(n * 4)
+        calc.generate(T(mem.ptr, abi.FP32, [n], mem_space=dev), abi.GEN_FILL, 0.0, 0.0)
+        calc.generate(T(src.ptr, abi.FP32, [n], mem_space=dev), abi.GEN_UNIFORM, -1.0, 1.0, seed=2)
+        step = lambda: calc.do_memory_write(T(mem.ptr, abi.FP32, [n], mem_space=dev), T(src.ptr, abi.FP32, [n], mem_space=dev), abi.RED_ADD, 0)  # noqa: E731
+    else:
+        out = alloc(n * 2)
+        step = lambda: calc.generate(T(out.ptr, abi.BF16, [n], mem_space=dev), abi.GEN_UNIFORM, -1.0, 1.0, seed=3)  # noqa: E731
+    steps = min(args.steps, 50)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    calc.sync()
+    launches0 = calc.launch_count()
+    sampler = ClockSampler(0)
+    calc.timer_start()
+    for _ in range(steps):
+        step()
+    ms = calc.timer_stop() / steps
+    clocks = sampler.stop()
+    launches = calc.launch_count() - launches0
+    peaks = measured_peaks()
+    alg = float(n) * wl["bytes_per_elem"]
+    gbs = alg / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "HBM GB/s (algorithmic bytes)", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
+        "config": {"workload": args.workload, "elements": n, "l2": "tensors of %d MiB exceed the 126 MB L2" % (alg / 2**20)},
+        "gpu_launches": launches, "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"], "traffic": None,
+                     "peak_note": "%s copy bandwidth" % peaks["source"], "algorithmic_bytes_per_launch": alg},
+    }))
+    for b in bufs:
+        b.free()
+    calc.close()
+
+
 def run_ours(args):
     import intel_gaudi3_software_b200 as pkg
     wl = WORKLOADS[args.workload]
+    if wl["kind"] == "stream":
+        return run_stream(args)
     rank, world, local, dist = dist_setup(args.gpus)
     calc = pkg.Calculator(device=local)
     if wl.get("exact"):

@@ -708,8 +708,9 @@ static int run_cast(mmeb200_ctx* c, void* out, uint32_t* acc, uint64_t n, const 
     const bool use_lfsr = random && rng != MMEB200_RNG_PHILOX && s.out_dtype != DT_FP32;
     if (!use_lfsr) {
         const bool philox = random && rng == MMEB200_RNG_PHILOX;
-        cast_kernel<<<grid_for(n, 256, c->sm_count), 256, 0, c->stream>>>(out, acc, n, s, philox ? 1 : 0, cp ? cp->rng_seed : 0,
-                                                                        cp ? cp->rng_offset : 0);
+        const int fast_bf16 = s.out_dtype == DT_BF16 && s.rm == RM_NE && !s.clip && !s.ftz && !s.clip_inf_in;
+        cast_kernel<<<grid_for((n + 3) / 4, 256, c->sm_count), 256, 0, c->stream>>>(out, acc, n, s, philox ? 1 : 0, cp ? cp->rng_seed : 0,
+                                                                                  cp ? cp->rng_offset : 0, fast_bf16);
         c->launches++;
         CUDA_OK(c, cudaGetLastError());
         return 0;
@@ -1508,7 +1509,7 @@ int mmeb200_compare(mmeb200_ctx* c, const mmeb200_tensor* a, const mmeb200_tenso
     p.spec = make_compare_spec(dt, int(b->fp_bias), b->inf_nan_mode, cd_size);
     p.mismatches = d;
     if (p.n) {
-        compare_kernel<<<grid_for(p.n, 256, c->sm_count), 256, 0, c->stream>>>(p);
+        compare_kernel<<<grid_for((p.n + 3) / 4, 256, c->sm_count), 256, 0, c->stream>>>(p);
         c->launches++;
         CUDA_OK(c, cudaGetLastError());
     }
@@ -1565,7 +1566,7 @@ int mmeb200_generate(mmeb200_ctx* c, mmeb200_tensor* out, const mmeb200_generate
     g.out_dtype = out->dtype == DT_FP32_IEEE ? DT_FP32 : out->dtype;
     if (g.out_dtype != DT_FP32 && g.out_dtype != DT_TF32) TRY(make_cast_spec(c, out, nullptr, &g.cast));
     if (g.n) {
-        generate_kernel<<<grid_for(g.n, 256, c->sm_count), 256, 0, c->stream>>>(g);
+        generate_kernel<<<grid_for((g.n + 3) / 4, 256, c->sm_count), 256, 0, c->stream>>>(g);
         c->launches++;
         CUDA_OK(c, cudaGetLastError());
     }
@@ -1663,7 +1664,7 @@ int mmeb200_memory_write(mmeb200_ctx* c, mmeb200_tensor* mem, const mmeb200_tens
         TRY(stage_in(c, mme_out, &so, true));
         TRY(stage_in(c, mem, &sm, true));
         if (n && mem->dtype == DT_FP32) {
-            memory_write_f32_kernel<<<grid_for(n, 256, c->sm_count), 256, 0, c->stream>>>(static_cast<uint32_t*>(sm.t.data),
+            memory_write_f32_kernel<<<grid_for((n + 3) / 4, 256, c->sm_count), 256, 0, c->stream>>>(static_cast<uint32_t*>(sm.t.data),
                                                                                          static_cast<const uint32_t*>(so.t.data), n,
                                                                                          red_op, red_rm, clip_fp);
             c->launches++;

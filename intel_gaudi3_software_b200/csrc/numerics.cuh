@@ -352,6 +352,14 @@ MME_HD uint32_t philox_word(uint64_t seed, uint64_t offset, uint64_t index) {
     return w ? w : 1u;
 }
 
+// The four words of elements 4q .. 4q+3 when offset is a multiple of 4: one Philox block instead of four.
+MME_HD void philox_words4(uint64_t seed, uint64_t offset, uint64_t index4, uint32_t (&w)[4]) {
+    const uint64_t ctr = (offset + index4) >> 2;
+    uint32_t c[4] = {uint32_t(ctr), uint32_t(ctr >> 32), 0u, 0u};
+    philox4x32_10(c, uint32_t(seed), uint32_t(seed >> 32));
+    for (int j = 0; j < 4; ++j) w[j] = c[j] ? c[j] : 1u;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Element comparison of the reference's TensorComparator
 // (mme/mme_reference/tensor_comparator_impl.cpp:26-105 limits, :414-438 rule, :441-492 ULP distance,
