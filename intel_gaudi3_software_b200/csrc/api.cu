@@ -415,7 +415,12 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     if (!o.has_cast) p.epi_mode = EPI_F32;
     else if (o.cast.out_dtype == DT_BF16 && o.cast.rm == RM_NE && !o.cast.relu && !o.cast.clip && !o.cast.ftz) p.epi_mode = EPI_BF16_RNE;
     else if (o.cast.out_dtype == DT_FP32 && !o.cast.relu && !o.cast.clip && !o.cast.ftz) p.epi_mode = EPI_F32;
-    else p.epi_mode = EPI_GENERIC;
+    else if (dtype_is_fp8(o.cast.out_dtype) && o.cast.rm == RM_NE && o.cast.clip && !o.cast.ftz && !o.cast.sftz &&
+             o.cast.mode == (o.cast.out_dtype == DT_FP8_143 ? 2 : 0)) {
+        // the output's Inf/NaN convention is the hardware fp8 format's: saturating hardware conversion after an exact rescale
+        p.epi_mode = EPI_FP8_HW;
+        p.hw_scale = ldexpf(1.0f, o.cast.bias - (o.cast.out_dtype == DT_FP8_143 ? 7 : 15));
+    } else p.epi_mode = EPI_GENERIC;
     p.rng_philox = o.philox;
     p.rng_seed = o.seed;
     p.rng_offset = o.offset;
@@ -454,7 +459,8 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
         const uint64_t pair_tiles = tiles * split;
         // a tile with few k blocks spends longer in its epilogue than in its MMAs: give it eight epilogue warps
         const uint32_t kb_per_tile = (p.num_k_blocks + split - 1) / split;
-        bool two_groups = kb_per_tile <= 12;
+        // ... and so does the general cast (stochastic rounding, fp8 output), hundreds of instructions per element
+        bool two_groups = kb_per_tile <= 12 || (split == 1 && p.epi_mode == EPI_GENERIC);
         if (const char* e = getenv("MME_B200_EPI_GROUPS")) two_groups = atoi(e) == 2;            // tuning knob
         if (two_groups)
             rc = j.kind == KIND_F16 ? launch_pair_kernel<KIND_F16, 2>(c, p, pair_tiles)

@@ -209,6 +209,91 @@ MME_HD uint32_t f32_to_bf16(uint32_t in, int rm, uint32_t rnd, bool clip, bool f
     return res & 0xFFFFu;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Straight-line forms of the two casts above for the GEMM epilogue, with the rounding mode a
+// template argument: no data-dependent branch, so the 32 conversions of one accumulator read
+// overlap instead of running one after another. They return the bits the general functions return
+// on every input (the fp8 form for the casts without a flush flag).
+// ---------------------------------------------------------------------------------------------
+template <int RM>
+MME_HD bool round_up_decision(bool msb, bool lsbs, bool odd, uint32_t sign, uint32_t rnd, uint32_t discarded) {
+    if (RM == RM_Z) return false;
+    if (RM == RM_UP) return sign == 0 && (msb || lsbs);
+    if (RM == RM_DOWN) return sign == 1 && (msb || lsbs);
+    if (RM == RM_HAZ) return msb;
+    if (RM == RM_SR) return discarded >= rnd;
+    return msb && (odd || lsbs);
+}
+
+// bf16 is the upper half of fp32, so rounding up is an integer increment of that half: the carry
+// runs from the mantissa into the exponent and from the largest finite value into infinity, for
+// normal and denormal values alike. Zero and infinity have no discarded bits and never round.
+template <int RM>
+MME_HD uint32_t f32_to_bf16_flat(uint32_t in, uint32_t rnd, bool clip, bool ftz, bool clip_inf_in) {
+    const uint32_t mag = in & 0x7FFFFFFFu, low = in & 0xFFFFu, sign = in >> 31;
+    const bool nan = mag > 0x7F800000u, inf = mag == 0x7F800000u;
+    bool up = false;
+    if (RM == RM_NE || RM == RM_UP || RM == RM_DOWN || RM == RM_HAZ || RM == RM_SR)
+        up = round_up_decision<RM>((low >> 15) != 0, (low & 0x7FFFu) != 0, ((in >> 16) & 1u) != 0, sign, rnd, low << 16);
+    up = up && mag != 0 && !inf;
+    uint32_t res = nan ? 0x7FFFu : (in >> 16) + (up ? 1u : 0u);
+    if (clip && (res & 0x7FFFu) == 0x7F80u && (clip_inf_in || !inf)) res -= 1;
+    if (ftz && (res & 0x7F80u) == 0 && (res & 0x7Fu) != 0) {
+        if (RM == RM_UP && (res >> 15) == 0) res = 0x0080u;
+        else if (RM == RM_DOWN && (res >> 15) == 1) res = 0x8080u;
+        else res &= 0x8000u;
+    }
+    return res & 0xFFFFu;
+}
+
+// fp8 without the two flush flags. Normal, subnormal and vanishing results share one formula: with
+// rc discarded bits (more of them the further the value lies below the smallest normal), the kept
+// bits, hidden one included, are rounded and added to the exponent field minus one, so that a carry
+// out of the mantissa steps the exponent and a subnormal that rounds up to 2^M becomes the smallest
+// normal. A magnitude that reaches `limit`, the first code past the largest binade, has overflowed
+// (by its exponent or by the rounding carry) and takes the value the output's Inf/NaN convention gives.
+template <int RM>
+MME_HD uint32_t f32_to_fp8_flat(uint32_t in, int exp_width, int B, uint32_t rnd, int mode, bool clip, bool clip_inf_in) {
+    constexpr int RM_SUB = (RM == RM_SR_NE_DNORM) ? RM_NE : RM;
+    constexpr int RM_NORM = (RM == RM_SR_NE_DNORM) ? RM_SR : RM;
+    const int M = 7 - exp_width;
+    const uint32_t exp_ones = (1u << exp_width) - 1u;
+    const int max_exp = int(exp_ones) - B - 1 + (mode != 0 ? 1 : 0);
+    const int min_norm_exp = 1 - B;
+    const uint32_t mag = in & 0x7FFFFFFFu, sign = in >> 31;
+    const bool nan = mag > 0x7F800000u, inf = mag == 0x7F800000u;
+    const bool toward_zero = RM == RM_Z || (sign && RM == RM_UP) || (!sign && RM == RM_DOWN);
+    const int ue = int(mag >> 23) - 127;
+    const uint32_t sig = mag ? ((in & 0x7FFFFFu) | 0x800000u) : 0u;
+    const int below = min_norm_exp - ue;
+    const bool sub = below > 0;
+    int rc = (22 - M) + (sub ? below : 0);
+    const bool vanishes = rc > 23;   // below half of the smallest subnormal: nothing is kept, and no bit counts as discarded
+    rc = rc > 25 ? 25 : rc;
+    const bool msb = ((sig >> rc) & 1u) != 0;
+    const bool lsbs = (sig & ((1u << rc) - 1u)) != 0;
+    const uint32_t discarded = vanishes ? 0u : (sig << (31 - rc));
+    uint32_t man = sig >> (rc + 1);
+    const bool odd = (man & 1u) != 0;
+    const bool up = (sub ? round_up_decision<RM_SUB>(msb, lsbs, odd, sign, rnd, discarded)
+                         : round_up_decision<RM_NORM>(msb, lsbs, odd, sign, rnd, discarded)) && mag != 0;
+    man += up ? 1u : 0u;
+    const int field_m1 = ue + B - 1;
+    uint32_t code = ((field_m1 > 0 ? uint32_t(field_m1) : 0u) << M) + man;
+    const uint32_t limit = uint32_t(max_exp + B + 1) << M;
+    const uint32_t inf_code = exp_ones << M;
+    if (code >= limit) code = mode == 0 ? (toward_zero ? limit - 1u : limit) : mode == 1 ? 0x7Fu : (toward_zero ? 0x7Eu : 0x7Fu);
+    else if (mode == 2 && toward_zero && code == 0x7Fu) code = 0x7Eu;
+    if (inf) code = mode == 0 ? inf_code : 0x7Fu;
+    uint32_t out = (sign << 7) | code;
+    if (nan) out = (mode == 2 ? (sign << 7) : 0u) | 0x7Fu;
+    if (clip && (clip_inf_in || !inf)) {
+        if (mode == 0 && (out & 0x7Fu) == inf_code) out -= 1u;
+        if (mode == 2 && (out & 0x7Fu) == 0x7Fu && !nan) out -= 1u;
+    }
+    return out & 0xFFu;
+}
+
 MME_HD uint32_t f32_to_f32(uint32_t in, int rm, bool clip, bool ftz) {
     uint32_t res = in;
     if (clip && f32_is_inf(res)) res -= 1;

@@ -9,6 +9,23 @@
 
 using namespace mmeb200;
 
+// the epilogue's straight-line casts (slow: reserved, always 0)
+template <int RM>
+static void cast_flat(const uint32_t* in, uint8_t* out, uint8_t* slow, size_t n, int out_dtype, int exp_width, int bias, int mode, int clip,
+                      int clip_inf_in, int ftz, const uint32_t* rnd)
+{
+    for (size_t i = 0; i < n; i++) {
+        if (out_dtype == DT_BF16) {
+            const uint32_t v = f32_to_bf16_flat<RM>(in[i], rnd[i], clip, ftz, clip_inf_in);
+            out[2 * i] = uint8_t(v);
+            out[2 * i + 1] = uint8_t(v >> 8);
+            slow[i] = 0;
+        } else {
+            out[i] = uint8_t(f32_to_fp8_flat<RM>(in[i], exp_width, bias, rnd[i], mode, clip, clip_inf_in));
+            slow[i] = 0;
+        }
+    }
+}
 extern "C" {
 void hc_fp8_decode(const uint8_t* in, uint32_t* out, size_t n, int exp_width, int bias, int mode)
 {
@@ -25,6 +42,16 @@ void hc_cast(const uint32_t* in, uint8_t* out, size_t n, int out_dtype, int exp_
         const uint32_t v = cast_from_f32(b, c, rnd ? rnd[i] : 0);
         for (int k = 0; k < es; k++) out[i * es + k] = uint8_t(v >> (8 * k));
     }
+}
+int hc_cast_flat(const uint32_t* in, uint8_t* out, uint8_t* slow, size_t n, int out_dtype, int exp_width, int bias, int mode, int rm, int clip,
+                 int clip_inf_in, int ftz, const uint32_t* rnd)
+{
+    switch (rm) {
+#define FLAT_CASE(R) case R: cast_flat<R>(in, out, slow, n, out_dtype, exp_width, bias, mode, clip, clip_inf_in, ftz, rnd); return 0;
+        FLAT_CASE(RM_NE) FLAT_CASE(RM_Z) FLAT_CASE(RM_UP) FLAT_CASE(RM_DOWN) FLAT_CASE(RM_SR) FLAT_CASE(RM_HAZ) FLAT_CASE(RM_SR_NE_DNORM)
+#undef FLAT_CASE
+    }
+    return -1;
 }
 void hc_compare(const uint8_t* a, const uint8_t* b, uint8_t* equal, size_t n, int dtype, int bias, int mode, unsigned cd)
 {

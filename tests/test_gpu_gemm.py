@@ -201,6 +201,18 @@ def test_fused_cast_matches_unfused(calc, port):
                 two = np.zeros(M * N, abi.NP_DTYPE[od])
                 calc.do_activation(T(two, od, [N, M], fp_bias=bias, inf_nan_mode=mode), T(acc.copy(), abi.FP32, [N, M]), cp)
                 assert (fused.view(np.uint8) == two.view(np.uint8)).all(), (od, rm, relu)
+    # counter-based stochastic rounding: the fused epilogue draws the words the cast kernel draws, at a stream position
+    # that is a multiple of four (one Philox block per four elements) and at one that is not; flush flags on and off
+    for od, bias, mode in ((abi.BF16, 0, 0), (abi.FP8_143, 7, 2), (abi.FP8_143, 3, 0), (abi.FP8_152, 15, 0), (abi.FP8_152, 30, 1)):
+        for rm in (abi.RM_SR, abi.RM_SR_NE_DNORM):
+            for offset, clip, ftz, sftz in ((0, 0, 0, 0), (17, 1, 0, 0), (8, 1, 1, 0), (4, 0, 0, 1)):
+                cp = abi.make_cast_params(rm, clip_fp=bool(clip), flush_denorms=bool(ftz), stochastic_ftz_fp8=bool(sftz), rng_kind=abi.RNG_PHILOX,
+                                          rng_seed=77, rng_offset=offset)
+                fused = np.zeros(M * N, abi.NP_DTYPE[od])
+                calc.do_batch_gemm(T(fused, od, [N, M], fp_bias=bias, inf_nan_mode=mode), x, w, abi.OP_AB, cp)
+                two = np.zeros(M * N, abi.NP_DTYPE[od])
+                calc.do_activation(T(two, od, [N, M], fp_bias=bias, inf_nan_mode=mode), T(acc.copy(), abi.FP32, [N, M]), cp)
+                assert (fused.view(np.uint8) == two.view(np.uint8)).all(), (od, bias, mode, rm, offset, clip, ftz, sftz)
     # LFSR stochastic rounding through bgemm == the reference's sequential order
     cp = abi.make_cast_params(abi.RM_SR, clip_fp=True)
     calc.set_lfsr(np.arange(2, 258, dtype=np.uint32), 37)
@@ -209,6 +221,44 @@ def test_fused_cast_matches_unfused(calc, port):
     want = np.zeros(M * N, np.uint16)
     rc, _ = port.activation(T(want, abi.BF16, [N, M]), T(acc.copy(), abi.FP32, [N, M]), cp, np.arange(2, 258, dtype=np.uint32), 37)
     assert rc == 0 and (fused == want).all()
+
+
+def test_fused_cast_over_the_whole_range(calc, port):
+    """The epilogue's straight-line casts against the oracle's cast of the same accumulators, on products that span every
+    binade of the fp8 formats: vanishing values, subnormals, the top binade, overflow, infinities and NaN in one tile."""
+    rng = np.random.default_rng(14)
+    M, N, K = 256, 512, 64
+    # one non-zero product per output: x row i holds 2^(i % 80 - 50) (+ sign), w is a random mantissa pattern
+    xf = np.zeros((M, K), np.float32)
+    xf[np.arange(M), np.arange(M) % K] = np.ldexp(1.0, (np.arange(M) % 80) - 50) * np.where(np.arange(M) & 1, -1, 1)
+    wf = rng.uniform(1.0, 2.0, (K, N)).astype(np.float32)
+    wf[:, 7] = 3.0e38      # times 2^k, k > 0: overflows fp32, the accumulator is an infinity
+    wf[:, 9] = np.nan
+    wf[:, 11] = 0.0
+    xb = (xf.view(np.uint32) >> 16).astype(np.uint16).ravel()
+    wb = (wf.view(np.uint32) >> 16).astype(np.uint16).ravel()
+    x, w = T(xb, abi.BF16, [K, M]), T(wb, abi.BF16, [N, K])
+    acc = np.zeros(M * N, np.float32)
+    calc.do_batch_gemm(T(acc, abi.FP32, [N, M]), x, w, abi.OP_AB)
+    bits = acc.view(np.uint32)
+    assert np.isinf(acc).any() and np.isnan(acc).any() and (acc == 0).any()
+    relu_bits = np.where((bits >> 31).astype(bool) | np.isnan(acc), np.uint32(0), bits)
+    rnd = np.zeros(M * N, np.uint32)
+    formats = ((abi.BF16, 0, 0, 0), (abi.FP8_143, 4, 7, 2), (abi.FP8_143, 4, 3, 2), (abi.FP8_143, 4, 11, 2), (abi.FP8_143, 4, 7, 0),
+               (abi.FP8_143, 4, 15, 1), (abi.FP8_152, 5, 15, 0), (abi.FP8_152, 5, 30, 0), (abi.FP8_152, 5, 1, 0), (abi.FP8_152, 5, 1, 2))
+    for od, ew, bias, mode in formats:
+        for rm in (0, 1, 2, 3, 6):
+            for clip, cii, relu in ((0, 0, 0), (1, 0, 0), (1, 1, 0), (1, 0, 1)):
+                cp = abi.make_cast_params(rm, relu=bool(relu), clip_fp=bool(clip), clip_inf_in=bool(cii))
+                fused = np.zeros(M * N, abi.NP_DTYPE[od])
+                calc.do_batch_gemm(T(fused, od, [N, M], fp_bias=bias, inf_nan_mode=mode), x, w, abi.OP_AB, cp)
+                src = relu_bits if relu else bits
+                if od == abi.BF16:
+                    want = port.fp32_to_bf16(src, rm, rnd, clip, 0, cii)
+                else:
+                    want = port.fp32_to_fp8(src, ew, bias, rm, rnd, 0, clip, cii, 0, mode)
+                bad = np.flatnonzero(fused != want)
+                assert bad.size == 0, (od, bias, mode, rm, clip, cii, relu, [(hex(src[i]), hex(fused[i]), hex(want[i])) for i in bad[:6]])
 
 
 def test_zero_common_dim_and_errors(calc):
