@@ -415,11 +415,15 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     if (!o.has_cast) p.epi_mode = EPI_F32;
     else if (o.cast.out_dtype == DT_BF16 && o.cast.rm == RM_NE && !o.cast.relu && !o.cast.clip && !o.cast.ftz) p.epi_mode = EPI_BF16_RNE;
     else if (o.cast.out_dtype == DT_FP32 && !o.cast.relu && !o.cast.clip && !o.cast.ftz) p.epi_mode = EPI_F32;
-    else if (dtype_is_fp8(o.cast.out_dtype) && o.cast.rm == RM_NE && o.cast.clip && !o.cast.ftz && !o.cast.sftz &&
+    else if (dtype_is_fp8(o.cast.out_dtype) && o.cast.rm == RM_NE && !o.cast.ftz && !o.cast.sftz &&
              o.cast.mode == (o.cast.out_dtype == DT_FP8_143 ? 2 : 0)) {
         // the output's Inf/NaN convention is the hardware fp8 format's: saturating hardware conversion after an exact rescale
+        const bool e4m3 = o.cast.out_dtype == DT_FP8_143;
         p.epi_mode = EPI_FP8_HW;
-        p.hw_scale = ldexpf(1.0f, o.cast.bias - (o.cast.out_dtype == DT_FP8_143 ? 7 : 15));
+        p.hw_scale = ldexpf(1.0f, o.cast.bias - (e4m3 ? 7 : 15));
+        // Nearest-even rounds past the largest finite value above 464 (1-4-3: the tie between 448 and 480 goes to the even
+        // 448) and from 61440 on (1-5-2: the tie between 57344 and 65536 goes to the even 65536).
+        p.hw_over = o.cast.clip ? INFINITY : (e4m3 ? 464.0f : nextafterf(61440.0f, 0.0f));
     } else p.epi_mode = EPI_GENERIC;
     p.rng_philox = o.philox;
     p.rng_seed = o.seed;

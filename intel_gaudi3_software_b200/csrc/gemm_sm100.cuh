@@ -83,6 +83,7 @@ struct GemmParams {
     uint64_t out_bstride[3]; // elements between batches
     float scale;
     float hw_scale;          // EPI_FP8_HW: 2^(output bias - the hardware format's bias)
+    float hw_over;           // EPI_FP8_HW: rescaled magnitudes above this overflow (infinity when the cast clips)
     CastSpec cast;
     uint32_t rng_philox;
     uint64_t rng_seed, rng_offset;
@@ -241,11 +242,12 @@ __device__ __forceinline__ void epilogue_convert(uint32_t (&v)[32], const GemmPa
             v[j] = f32_is_nan(bits) ? kF32CanonNan : bits;
         }
     } else if (p.epi_mode == EPI_FP8_HW) {
-        // Round-to-nearest-even with clipping into fp8 whose Inf/NaN convention is the hardware format's (1-4-3: no
-        // infinity, 0x7F the only NaN; 1-5-2: IEEE-like): the saturating hardware conversion gives the reference's bits
-        // once the value is rescaled from the tensor's exponent bias to the format's own (an exact power of two), for
-        // subnormal results too. An infinite input is the one case it does not cover (it saturates; the reference keeps
-        // the infinity, or the NaN code where the format has none, unless infinities are clipped as well).
+        // Round-to-nearest-even into fp8 whose Inf/NaN convention is the hardware format's (1-4-3: no infinity, 0x7F the
+        // only NaN; 1-5-2: IEEE-like): the saturating hardware conversion gives the reference's bits once the value is
+        // rescaled from the tensor's exponent bias to the format's own (an exact power of two), for subnormal results
+        // too. Two cases are patched afterwards: without clipping, a magnitude that rounds past the largest finite value
+        // becomes the infinity (the NaN code where the format has none) instead of saturating; with clipping, an
+        // infinite input stays one unless infinities are clipped as well.
         const bool e5m2 = p.cast.out_dtype == DT_FP8_152, relu = p.cast.relu != 0, keep_inf = !p.cast.clip_inf_in;
         const uint32_t inf_code = e5m2 ? 0x7Cu : 0x7Fu;
 #pragma unroll
@@ -256,11 +258,11 @@ __device__ __forceinline__ void epilogue_convert(uint32_t (&v)[32], const GemmPa
             for (int e = 0; e < 4; ++e) {
                 float x = __uint_as_float(v[4 * q + e]) * p.scale;
                 if (relu) x = x > 0.0f ? x : 0.0f;          // NaN and -0 become +0, as std::max(0.f, x)
-                if (keep_inf && fabsf(x) == __int_as_float(0x7F800000)) {
+                f[e] = x * p.hw_scale;
+                if (fabsf(f[e]) > p.hw_over || (keep_inf && fabsf(x) == __int_as_float(0x7F800000))) {
                     fix_mask |= 0xFFu << (8 * e);
                     fix_val |= (((__float_as_uint(x) >> 24) & 0x80u) | inf_code) << (8 * e);
                 }
-                f[e] = x * p.hw_scale;
             }
             uint16_t lo, hi;
             if (e5m2) {
