@@ -209,14 +209,10 @@ __device__ __noinline__ void epilogue_cast_any(uint32_t (&v)[32], const GemmPara
     const bool stream_ok = !p.rng_philox || ((p.rng_offset + flat_index) & 3u) == 0;
     if (stream_ok && dtype_is_fp8(p.cast.out_dtype) && !p.cast.ftz && !p.cast.sftz) {
         switch (p.cast.rm) {
-            case RM_NE: epilogue_fp8_flat<RM_NE>(v, p, flat_index); return;
-            case RM_Z: epilogue_fp8_flat<RM_Z>(v, p, flat_index); return;
             case RM_UP: epilogue_fp8_flat<RM_UP>(v, p, flat_index); return;
             case RM_DOWN: epilogue_fp8_flat<RM_DOWN>(v, p, flat_index); return;
-            case RM_SR: epilogue_fp8_flat<RM_SR>(v, p, flat_index); return;
             case RM_HAZ: epilogue_fp8_flat<RM_HAZ>(v, p, flat_index); return;
-            case RM_SR_NE_DNORM: epilogue_fp8_flat<RM_SR_NE_DNORM>(v, p, flat_index); return;
-            default: break;
+            default: break;   // the inlined modes arrive here only with an unaligned random stream
         }
     }
     epilogue_general(v, p, out_elem, flat_index);
@@ -287,6 +283,17 @@ __device__ __forceinline__ void epilogue_convert(uint32_t (&v)[32], const GemmPa
                 default: epilogue_bf16_flat<RM_Z>(v, p, flat_index); break;   // every other mode truncates
             }
             return;
+        }
+        // fp8 in the common rounding modes, inlined as well (out of line, through local memory, stochastic rounding
+        // measured 0.67 ms on 8192^3 against 0.40 ms inlined); the rarer modes stay out of line to bound the build time
+        if (dtype_is_fp8(p.cast.out_dtype) && !p.cast.ftz && !p.cast.sftz && (!p.rng_philox || ((p.rng_offset + flat_index) & 3u) == 0)) {
+            switch (p.cast.rm) {
+                case RM_NE: epilogue_fp8_flat<RM_NE>(v, p, flat_index); return;
+                case RM_Z: epilogue_fp8_flat<RM_Z>(v, p, flat_index); return;
+                case RM_SR: epilogue_fp8_flat<RM_SR>(v, p, flat_index); return;
+                case RM_SR_NE_DNORM: epilogue_fp8_flat<RM_SR_NE_DNORM>(v, p, flat_index); return;
+                default: break;
+            }
         }
         uint32_t t[32];
 #pragma unroll
