@@ -657,10 +657,25 @@ __global__ void compare_kernel(CompareParams p) {
         // 16 bytes of each tensor per thread and iteration
         const uint32_t per = 16 / p.elem;
         const uint64_t nv = p.n / per;
+        // Bit-identical elements compare equal unless they are NaN (zero difference passes the all-close rule, equal
+        // infinities the ULP rule), so sixteen identical bytes without a NaN need no arithmetic. NaN test on packed
+        // elements: added to an element's magnitude bits, nan_add carries into its sign position iff it is a NaN.
+        uint32_t mag_mask, nan_add;
+        if (p.elem == 4) { mag_mask = 0x7FFFFFFFu; nan_add = 0x007FFFFFu; }
+        else if (p.elem == 2) { mag_mask = 0x7FFF7FFFu; nan_add = 0x007F007Fu; }
+        else {
+            mag_mask = 0x7F7F7F7Fu;
+            nan_add = p.spec.mode == 1 ? 0u : p.spec.mode == 2 ? 0x01010101u : (p.spec.dtype == DT_FP8_143 ? 0x07070707u : 0x03030303u);
+        }
         for (uint64_t q = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; q < nv; q += stride) {
             const uint4 va = reinterpret_cast<const uint4*>(p.a)[q], vb = reinterpret_cast<const uint4*>(p.b)[q];
             const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
-            if (p.bit_exact && va.x == vb.x && va.y == vb.y && va.z == vb.z && va.w == vb.w) continue;
+            if (va.x == vb.x && va.y == vb.y && va.z == vb.z && va.w == vb.w) {
+                if (p.bit_exact) continue;
+                const uint32_t carries = (((va.x & mag_mask) + nan_add) | ((va.y & mag_mask) + nan_add) | ((va.z & mag_mask) + nan_add) |
+                                          ((va.w & mag_mask) + nan_add)) & ~mag_mask;
+                if (carries == 0) continue;
+            }
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
                 for (uint32_t e = 0; e < 4u / p.elem; ++e) {

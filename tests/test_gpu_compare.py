@@ -36,6 +36,23 @@ def test_verdicts_match_reference(calc, ref, dtype, bias, mode):
         assert left < bad.size
 
 
+@pytest.mark.parametrize("dtype,bias,mode", FORMATS + ((abi.FP8_143, 7, 1), (abi.FP8_152, 15, 1), (abi.FP8_152, 15, 2), (abi.FP8_143, 11, 0)))
+def test_identical_tensors_differ_only_at_nan(calc, ref, dtype, bias, mode):
+    """A tensor against its own copy: sixteen identical bytes skip the arithmetic unless one of them is a NaN, which never
+    compares equal -- every bit pattern of every format, NaN codes of each Inf/NaN convention included."""
+    rng = np.random.default_rng(8)
+    n = 1 << 16
+    size = np.dtype(abi.NP_DTYPE[dtype]).itemsize
+    a = rng.integers(0, 2 ** (8 * size), n, dtype=np.uint64).astype({1: np.uint8, 2: np.uint16, 4: np.uint32}[size])   # raw bit patterns
+    equal = ref.compare_elements(dtype, bias, mode, 64, a, a.copy())
+    bad = np.nonzero(equal == 0)[0]
+    got, first = calc.compare(T(a, dtype, [n], fp_bias=bias, inf_nan_mode=mode), T(a.copy(), dtype, [n], fp_bias=bias, inf_nan_mode=mode), 64)
+    assert got == bad.size
+    assert first == (bad[0] if bad.size else 2**64 - 1)
+    if mode != 1:
+        assert bad.size > 0
+
+
 @pytest.mark.parametrize("dtype", (abi.FP32, abi.BF16))
 def test_partial_sums(calc, ref, dtype):
     rng = np.random.default_rng(6)
