@@ -67,6 +67,8 @@ WORKLOADS = {
 # value = algorithmic GB/s (bytes each kernel must read and write once); they run on tensors far larger than L2.
 STREAM_WORKLOADS = {
     "cast_f32_to_bf16": dict(kind="stream", n=1 << 28, bytes_per_elem=6, dtype="f32"),          # doActivation, RNE
+    "cast_f32_to_fp8": dict(kind="stream", n=1 << 28, bytes_per_elem=5, dtype="f32"),           # doActivation, fp8_143 RNE + clip
+    "cast_f32_to_bf16_sr": dict(kind="stream", n=1 << 28, bytes_per_elem=6, dtype="f32"),       # doActivation, stochastic (Philox)
     "compare_bf16": dict(kind="stream", n=1 << 29, bytes_per_elem=4, dtype="bf16"),             # TensorComparator rule
     "memory_write_add_f32": dict(kind="stream", n=1 << 28, bytes_per_elem=12, dtype="f32"),     # doMemoryWrite add: 2 reads + 1 write
     "generate_uniform_bf16": dict(kind="stream", n=1 << 29, bytes_per_elem=2, dtype="bf16"),    # RandomSimTensorGenerator
@@ -261,6 +263,13 @@ def run_stream(args):
         calc.generate(T(src.ptr, abi.FP32, [n], mem_space=dev), abi.GEN_NORMAL, -100.0, 100.0, 0.0, 1.0, seed=1)
         cp = abi.make_cast_params(abi.RM_NE)
         step = lambda: calc.do_activation(T(dst.ptr, abi.BF16, [n], mem_space=dev), T(src.ptr, abi.FP32, [n], mem_space=dev), cp)  # noqa: E731
+    elif args.workload in ("cast_f32_to_fp8", "cast_f32_to_bf16_sr"):
+        fp8 = args.workload == "cast_f32_to_fp8"
+        src, dst = alloc(n * 4), alloc(n * (1 if fp8 else 2))
+        calc.generate(T(src.ptr, abi.FP32, [n], mem_space=dev), abi.GEN_NORMAL, -100.0, 100.0, 0.0, 1.0, seed=1)
+        cp = abi.make_cast_params(abi.RM_NE, clip_fp=True) if fp8 else abi.make_cast_params(abi.RM_SR, rng_kind=abi.RNG_PHILOX, rng_seed=9)
+        to = T(dst.ptr, abi.FP8_143, [n], fp_bias=7, inf_nan_mode=abi.INFNAN_MINIMAL, mem_space=dev) if fp8 else T(dst.ptr, abi.BF16, [n], mem_space=dev)
+        step = lambda: calc.do_activation(to, T(src.ptr, abi.FP32, [n], mem_space=dev), cp)  # noqa: E731
     elif args.workload == "compare_bf16":
         a, b = alloc(n * 2), alloc(n * 2)
         for buf, seed in ((a, 1), (b, 1)):

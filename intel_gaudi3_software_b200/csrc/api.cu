@@ -340,6 +340,15 @@ struct GemmJob {
     int force_split = 0;
 };
 
+// Rescale and overflow threshold of the hardware fp8 conversion (f32x4_to_fp8_hw) for a cast that cast_is_fp8_hw accepts.
+static void fp8_hw_constants(const CastSpec& s, float* scale, float* over) {
+    const bool e4m3 = s.out_dtype == DT_FP8_143;
+    *scale = ldexpf(1.0f, s.bias - (e4m3 ? 7 : 15));
+    // Nearest-even rounds past the largest finite value above 464 (1-4-3: the tie between 448 and 480 goes to the even
+    // 448) and from 61440 on (1-5-2: the tie between 57344 and 65536 goes to the even 65536).
+    *over = s.clip ? INFINITY : (e4m3 ? 464.0f : nextafterf(61440.0f, 0.0f));
+}
+
 static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     GemmParams p;
     memset(&p, 0, sizeof p);
@@ -415,15 +424,10 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     if (!o.has_cast) p.epi_mode = EPI_F32;
     else if (o.cast.out_dtype == DT_BF16 && o.cast.rm == RM_NE && !o.cast.relu && !o.cast.clip && !o.cast.ftz) p.epi_mode = EPI_BF16_RNE;
     else if (o.cast.out_dtype == DT_FP32 && !o.cast.relu && !o.cast.clip && !o.cast.ftz) p.epi_mode = EPI_F32;
-    else if (dtype_is_fp8(o.cast.out_dtype) && o.cast.rm == RM_NE && !o.cast.ftz && !o.cast.sftz &&
-             o.cast.mode == (o.cast.out_dtype == DT_FP8_143 ? 2 : 0)) {
+    else if (cast_is_fp8_hw(o.cast)) {
         // the output's Inf/NaN convention is the hardware fp8 format's: saturating hardware conversion after an exact rescale
-        const bool e4m3 = o.cast.out_dtype == DT_FP8_143;
         p.epi_mode = EPI_FP8_HW;
-        p.hw_scale = ldexpf(1.0f, o.cast.bias - (e4m3 ? 7 : 15));
-        // Nearest-even rounds past the largest finite value above 464 (1-4-3: the tie between 448 and 480 goes to the even
-        // 448) and from 61440 on (1-5-2: the tie between 57344 and 65536 goes to the even 65536).
-        p.hw_over = o.cast.clip ? INFINITY : (e4m3 ? 464.0f : nextafterf(61440.0f, 0.0f));
+        fp8_hw_constants(o.cast, &p.hw_scale, &p.hw_over);
     } else p.epi_mode = EPI_GENERIC;
     p.rng_philox = o.philox;
     p.rng_seed = o.seed;
@@ -718,9 +722,15 @@ static int run_cast(mmeb200_ctx* c, void* out, uint32_t* acc, uint64_t n, const 
     const bool use_lfsr = random && rng != MMEB200_RNG_PHILOX && s.out_dtype != DT_FP32;
     if (!use_lfsr) {
         const bool philox = random && rng == MMEB200_RNG_PHILOX;
-        const int fast_bf16 = s.out_dtype == DT_BF16 && s.rm == RM_NE && !s.clip && !s.ftz && !s.clip_inf_in;
-        cast_kernel<<<grid_for((n + 3) / 4, 256, c->sm_count), 256, 0, c->stream>>>(out, acc, n, s, philox ? 1 : 0, cp ? cp->rng_seed : 0,
-                                                                                  cp ? cp->rng_offset : 0, fast_bf16);
+        const uint64_t offset = cp ? cp->rng_offset : 0;
+        CastTier tier = {CAST_GENERAL, 1.0f, INFINITY};
+        if (s.out_dtype == DT_BF16 && s.rm == RM_NE && !s.clip && !s.ftz && !s.clip_inf_in) tier.kind = CAST_BF16_RNE;
+        else if (cast_is_fp8_hw(s)) {
+            tier.kind = CAST_FP8_HW;
+            fp8_hw_constants(s, &tier.hw_scale, &tier.hw_over);
+        } else if ((!philox || (offset & 3u) == 0) && (s.out_dtype == DT_BF16 || (dtype_is_fp8(s.out_dtype) && !s.ftz && !s.sftz)))
+            tier.kind = CAST_FLAT;
+        cast_kernel<<<grid_for((n + 15) / 16, 256, c->sm_count), 256, 0, c->stream>>>(out, acc, n, s, philox ? 1 : 0, cp ? cp->rng_seed : 0, offset, tier);
         c->launches++;
         CUDA_OK(c, cudaGetLastError());
         return 0;

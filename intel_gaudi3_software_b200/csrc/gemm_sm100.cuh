@@ -238,38 +238,17 @@ __device__ __forceinline__ void epilogue_convert(uint32_t (&v)[32], const GemmPa
             v[j] = f32_is_nan(bits) ? kF32CanonNan : bits;
         }
     } else if (p.epi_mode == EPI_FP8_HW) {
-        // Round-to-nearest-even into fp8 whose Inf/NaN convention is the hardware format's (1-4-3: no infinity, 0x7F the
-        // only NaN; 1-5-2: IEEE-like): the saturating hardware conversion gives the reference's bits once the value is
-        // rescaled from the tensor's exponent bias to the format's own (an exact power of two), for subnormal results
-        // too. Two cases are patched afterwards: without clipping, a magnitude that rounds past the largest finite value
-        // becomes the infinity (the NaN code where the format has none) instead of saturating; with clipping, an
-        // infinite input stays one unless infinities are clipped as well.
+        // hardware conversion after an exact rescale (f32x4_to_fp8_hw)
         const bool e5m2 = p.cast.out_dtype == DT_FP8_152, relu = p.cast.relu != 0, keep_inf = !p.cast.clip_inf_in;
-        const uint32_t inf_code = e5m2 ? 0x7Cu : 0x7Fu;
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
-            float f[4];
-            uint32_t fix_mask = 0u, fix_val = 0u;
+            float x[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                float x = __uint_as_float(v[4 * q + e]) * p.scale;
-                if (relu) x = x > 0.0f ? x : 0.0f;          // NaN and -0 become +0, as std::max(0.f, x)
-                f[e] = x * p.hw_scale;
-                if (fabsf(f[e]) > p.hw_over || (keep_inf && fabsf(x) == __int_as_float(0x7F800000))) {
-                    fix_mask |= 0xFFu << (8 * e);
-                    fix_val |= (((__float_as_uint(x) >> 24) & 0x80u) | inf_code) << (8 * e);
-                }
+                x[e] = __uint_as_float(v[4 * q + e]) * p.scale;
+                if (relu) x[e] = x[e] > 0.0f ? x[e] : 0.0f;          // NaN and -0 become +0, as std::max(0.f, x)
             }
-            uint16_t lo, hi;
-            if (e5m2) {
-                asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(f[1]), "f"(f[0]));
-                asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(f[3]), "f"(f[2]));
-            } else {
-                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(f[1]), "f"(f[0]));
-                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(f[3]), "f"(f[2]));
-            }
-            const uint32_t w = uint32_t(lo) | (uint32_t(hi) << 16);
-            v[q] = (w & ~fix_mask) | fix_val;               // word q lies below every value still to be read
+            v[q] = f32x4_to_fp8_hw(x, e5m2, p.hw_scale, p.hw_over, keep_inf);   // word q lies below every value still to be read
         }
     } else {
         // bf16 in the other rounding modes: some twenty instructions per element, inlined on the accumulator registers
