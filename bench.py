@@ -45,6 +45,11 @@ WORKLOADS = {
     # config 2 with the seeded stochastic-rounding cast (counter-based stream, fused into the epilogue)
     "fp8_gemm_8192_sr": dict(kind="gemm", M=8192, N=8192, K=8192, in_dtype=abi.FP8_143, w_dtype=abi.FP8_143, bias=7,
                              out_dtype=abi.BF16, bound="tensor", peak_scale=2.0, dtype="fp8_143", stochastic=True),
+    # config 2 with fp8_143 output: round-to-nearest-even + clipping (hardware conversion), and stochastic rounding
+    "fp8_gemm_8192_fp8out": dict(kind="gemm", M=8192, N=8192, K=8192, in_dtype=abi.FP8_143, w_dtype=abi.FP8_143, bias=7,
+                                 out_dtype=abi.FP8_143, bound="tensor", peak_scale=2.0, dtype="fp8_143", clip=True),
+    "fp8_gemm_8192_fp8out_sr": dict(kind="gemm", M=8192, N=8192, K=8192, in_dtype=abi.FP8_143, w_dtype=abi.FP8_143, bias=7,
+                                    out_dtype=abi.FP8_143, bound="tensor", peak_scale=2.0, dtype="fp8_143", stochastic=True),
     "bf16_gemm_8192": dict(kind="gemm", M=8192, N=8192, K=8192, in_dtype=abi.BF16, w_dtype=abi.BF16, bias=0,
                            out_dtype=abi.BF16, bound="tensor", peak_scale=1.0, dtype="bf16"),
     "bf16_gemm_1024": dict(kind="gemm", M=1024, N=1024, K=1024, in_dtype=abi.BF16, w_dtype=abi.BF16, bias=0,
@@ -325,6 +330,8 @@ def run_ours(args):
     cast = abi.make_cast_params(abi.RM_NE) if wl["out_dtype"] != abi.FP32 else None
     if wl.get("stochastic"):
         cast = abi.make_cast_params(abi.RM_SR, clip_fp=True, rng_kind=abi.RNG_PHILOX, rng_seed=2024)
+    elif wl.get("clip"):
+        cast = abi.make_cast_params(abi.RM_NE, clip_fp=True)
 
     # ---- operands, resident in HBM (each rank: its own shard, seeded by rank)
     host = synth_inputs(wl, seed=1000 + rank)
@@ -344,7 +351,7 @@ def run_ours(args):
         dout = calc.alloc(out_bytes)
 
         def tensors(px, pw, po, space):
-            return (T(po, wl["out_dtype"], os_, mem_space=space),
+            return (T(po, wl["out_dtype"], os_, fp_bias=7 if wl["out_dtype"] == abi.FP8_143 else 15, inf_nan_mode=mode(wl["out_dtype"]), mem_space=space),
                     T(px, wl["in_dtype"], xs, fp_bias=x_bias, inf_nan_mode=mode(wl["in_dtype"]), mem_space=space),
                     T(pw, wl["w_dtype"], ws, fp_bias=w_bias, inf_nan_mode=mode(wl["w_dtype"]), mem_space=space))
         to, tx, tw = tensors(dev[0].ptr, dev[1].ptr, dout.ptr, abi.MEM_DEVICE)
@@ -489,7 +496,9 @@ def run_ours(args):
         "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
         "config": {"workload": args.workload, "per_gpu": {k: v for k, v in wl.items() if k in ("M", "N", "K", "batch")} or CONV,
                    "accumulate": "Gaudi3 tree, bit-exact (integer emulation, no tensor cores: the tensor peak is shown for scale only)" if wl.get("exact") else "fp32",
-                   "output": ("bf16 stochastic rounding (Philox)" if wl.get("stochastic") else "bf16 RNE") if wl["out_dtype"] == abi.BF16 else "fp32",
+                   "output": {abi.BF16: "bf16", abi.FP8_143: "fp8_143", abi.FP32: "fp32"}[wl["out_dtype"]] +
+                             ("" if wl["out_dtype"] == abi.FP32 else " stochastic rounding (Philox)" if wl.get("stochastic") else
+                              " RNE + clip" if wl.get("clip") else " RNE"),
                    "l2": "operands + output (%d MiB) exceed the 126 MB L2; no flush between steps" % ((in_bytes + out_bytes) >> 20)
                    if in_bytes + out_bytes > L2_BYTES else "working set fits L2 (latency-bound correctness config)",
                    "sharding": "rows of A / images per rank, replica of B / weights" if wl.get("op") != abi.OP_DEDW else
