@@ -340,15 +340,6 @@ struct GemmJob {
     int force_split = 0;
 };
 
-// Rescale and overflow threshold of the hardware fp8 conversion (f32x4_to_fp8_hw) for a cast that cast_is_fp8_hw accepts.
-static void fp8_hw_constants(const CastSpec& s, float* scale, float* over) {
-    const bool e4m3 = s.out_dtype == DT_FP8_143;
-    *scale = ldexpf(1.0f, s.bias - (e4m3 ? 7 : 15));
-    // Nearest-even rounds past the largest finite value above 464 (1-4-3: the tie between 448 and 480 goes to the even
-    // 448) and from 61440 on (1-5-2: the tie between 57344 and 65536 goes to the even 65536).
-    *over = s.clip ? INFINITY : (e4m3 ? 464.0f : nextafterf(61440.0f, 0.0f));
-}
-
 static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     GemmParams p;
     memset(&p, 0, sizeof p);
@@ -427,7 +418,7 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     else if (cast_is_fp8_hw(o.cast)) {
         // the output's Inf/NaN convention is the hardware fp8 format's: saturating hardware conversion after an exact rescale
         p.epi_mode = EPI_FP8_HW;
-        fp8_hw_constants(o.cast, &p.hw_scale, &p.hw_over);
+        p.hw = fp8_hw_cast(o.cast);
     } else p.epi_mode = EPI_GENERIC;
     p.rng_philox = o.philox;
     p.rng_seed = o.seed;
@@ -468,7 +459,7 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
         // a tile with few k blocks spends longer in its epilogue than in its MMAs: give it eight epilogue warps
         const uint32_t kb_per_tile = (p.num_k_blocks + split - 1) / split;
         // ... and so does the general cast (stochastic rounding, fp8 output), hundreds of instructions per element
-        bool two_groups = kb_per_tile <= 12 || (split == 1 && p.epi_mode == EPI_GENERIC);
+        bool two_groups = kb_per_tile <= 12 || (split == 1 && (p.epi_mode == EPI_GENERIC || p.epi_mode == EPI_FP8_HW));
         if (const char* e = getenv("MME_B200_EPI_GROUPS")) two_groups = atoi(e) == 2;            // tuning knob
         if (two_groups)
             rc = j.kind == KIND_F16 ? launch_pair_kernel<KIND_F16, 2>(c, p, pair_tiles)
@@ -723,11 +714,13 @@ static int run_cast(mmeb200_ctx* c, void* out, uint32_t* acc, uint64_t n, const 
     if (!use_lfsr) {
         const bool philox = random && rng == MMEB200_RNG_PHILOX;
         const uint64_t offset = cp ? cp->rng_offset : 0;
-        CastTier tier = {CAST_GENERAL, 1.0f, INFINITY};
+        CastTier tier;
+        memset(&tier, 0, sizeof tier);
+        tier.kind = CAST_GENERAL;
         if (s.out_dtype == DT_BF16 && s.rm == RM_NE && !s.clip && !s.ftz && !s.clip_inf_in) tier.kind = CAST_BF16_RNE;
         else if (cast_is_fp8_hw(s)) {
             tier.kind = CAST_FP8_HW;
-            fp8_hw_constants(s, &tier.hw_scale, &tier.hw_over);
+            tier.hw = fp8_hw_cast(s);
         } else if ((!philox || (offset & 3u) == 0) && (s.out_dtype == DT_BF16 || (dtype_is_fp8(s.out_dtype) && !s.ftz && !s.sftz)))
             tier.kind = CAST_FLAT;
         cast_kernel<<<grid_for((n + 15) / 16, 256, c->sm_count), 256, 0, c->stream>>>(out, acc, n, s, philox ? 1 : 0, cp ? cp->rng_seed : 0, offset, tier);

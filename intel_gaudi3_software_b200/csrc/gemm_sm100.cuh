@@ -82,8 +82,7 @@ struct GemmParams {
     uint64_t out_ld;         // elements between output rows
     uint64_t out_bstride[3]; // elements between batches
     float scale;
-    float hw_scale;          // EPI_FP8_HW: 2^(output bias - the hardware format's bias)
-    float hw_over;           // EPI_FP8_HW: rescaled magnitudes above this overflow (infinity when the cast clips)
+    Fp8HwCast hw;            // EPI_FP8_HW
     CastSpec cast;
     uint32_t rng_philox;
     uint64_t rng_seed, rng_offset;
@@ -239,16 +238,17 @@ __device__ __forceinline__ void epilogue_convert(uint32_t (&v)[32], const GemmPa
         }
     } else if (p.epi_mode == EPI_FP8_HW) {
         // hardware conversion after an exact rescale (f32x4_to_fp8_hw)
-        const bool e5m2 = p.cast.out_dtype == DT_FP8_152, relu = p.cast.relu != 0, keep_inf = !p.cast.clip_inf_in;
+        const bool relu = p.cast.relu != 0;
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
             float x[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 x[e] = __uint_as_float(v[4 * q + e]) * p.scale;
+                if (x[e] != x[e]) x[e] = __uint_as_float(kF32CanonNan);   // the accumulator's NaN is canonical (positive)
                 if (relu) x[e] = x[e] > 0.0f ? x[e] : 0.0f;          // NaN and -0 become +0, as std::max(0.f, x)
             }
-            v[q] = f32x4_to_fp8_hw(x, e5m2, p.hw_scale, p.hw_over, keep_inf);   // word q lies below every value still to be read
+            v[q] = f32x4_to_fp8_hw(x, p.hw);   // word q lies below every value still to be read
         }
     } else {
         // bf16 in the other rounding modes: some twenty instructions per element, inlined on the accumulator registers

@@ -24,7 +24,7 @@ __device__ __forceinline__ void store_cast(void* out, uint64_t i, uint32_t v, in
 enum : int { CAST_GENERAL = 0, CAST_BF16_RNE = 1, CAST_FP8_HW = 2, CAST_FLAT = 3 };
 struct CastTier {
     int kind;
-    float hw_scale, hw_over;   // CAST_FP8_HW
+    Fp8HwCast hw;   // CAST_FP8_HW
 };
 
 // Four fp32 values (ReLU applied) to packed outputs: 4, 2 or 1 words in w.
@@ -36,7 +36,7 @@ __device__ __forceinline__ void cast_group4(const uint32_t (&b)[4], const uint32
     }
     if (t.kind == CAST_FP8_HW) {
         const float x[4] = {__uint_as_float(b[0]), __uint_as_float(b[1]), __uint_as_float(b[2]), __uint_as_float(b[3])};
-        w[0] = f32x4_to_fp8_hw(x, c.out_dtype == DT_FP8_152, t.hw_scale, t.hw_over, !c.clip_inf_in);
+        w[0] = f32x4_to_fp8_hw(x, t.hw);
         return;
     }
     uint32_t o[4];

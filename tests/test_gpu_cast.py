@@ -18,6 +18,14 @@ def accumulators(n, seed=0):
     rng = np.random.default_rng(seed)
     acc = (rng.normal(0, 1, n) * 10.0 ** rng.integers(-9, 9, n)).astype(np.float32)
     acc[:10] = [0, -0.0, np.inf, -np.inf, np.nan, 1e-45, 3e38, -3e38, 448.0, 464.0]
+    # the top of each fp8 flavour at bias 7 / 15 (largest finite values, rounding ties, first overflowing values), both signs,
+    # scaled to the other biases of FORMATS as well; and a negative NaN
+    edges = np.array([240, 247.99, 248, 248.01, 256, 448, 463.99, 464, 464.01, 480, 495.99, 496, 512, 57344, 61439.9, 61440, 65536, 114688, 122880],
+                     np.float32)
+    tops = np.concatenate([edges * s for s in (1.0, 2.0 ** -4, 2.0 ** 4, 2.0 ** -2, 2.0 ** -5, 2.0 ** -15)])
+    acc[10:10 + tops.size] = tops
+    acc[10 + tops.size:10 + 2 * tops.size] = -tops
+    acc.view(np.uint32)[10 + 2 * tops.size] = 0xFFC00001
     return acc
 
 

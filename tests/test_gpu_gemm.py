@@ -244,7 +244,7 @@ def test_fused_cast_over_the_whole_range(calc, port):
     assert np.isinf(acc).any() and np.isnan(acc).any() and (acc == 0).any()
     relu_bits = np.where((bits >> 31).astype(bool) | np.isnan(acc), np.uint32(0), bits)
     rnd = np.zeros(M * N, np.uint32)
-    formats = ((abi.BF16, 0, 0, 0), (abi.FP8_143, 4, 7, 2), (abi.FP8_143, 4, 3, 2), (abi.FP8_143, 4, 11, 2), (abi.FP8_143, 4, 7, 0),
+    formats = ((abi.BF16, 0, 0, 0), (abi.FP8_143, 4, 7, 2), (abi.FP8_143, 4, 3, 2), (abi.FP8_143, 4, 11, 2), (abi.FP8_143, 4, 7, 0), (abi.FP8_143, 4, 3, 0), (abi.FP8_143, 4, 9, 1),
                (abi.FP8_143, 4, 15, 1), (abi.FP8_152, 5, 15, 0), (abi.FP8_152, 5, 30, 0), (abi.FP8_152, 5, 1, 0), (abi.FP8_152, 5, 1, 2))
     for od, ew, bias, mode in formats:
         for rm in (0, 1, 2, 3, 6):
