@@ -53,6 +53,26 @@ int hc_cast_flat(const uint32_t* in, uint8_t* out, uint8_t* slow, size_t n, int 
     }
     return -1;
 }
+// Host model of the hardware fp8 path (f32x4_to_fp8_hw): the product's rescale, thresholds and constant codes (fp8_hw_cast,
+// fp8_hw_fix) around a model of the saturating hardware conversion -- round-to-nearest-even into the hardware format's own
+// bias and Inf/NaN convention with everything above the largest finite value clamped to it.
+int hc_cast_fp8_hw_model(const uint32_t* in, uint8_t* out, size_t n, int out_dtype, int exp_width, int bias, int mode, int clip, int clip_inf_in)
+{
+    CastSpec c{out_dtype, exp_width, bias, mode, RM_NE, 0, clip, clip_inf_in, 0, 0};
+    if (!cast_is_fp8_hw(c)) return -1;
+    const Fp8HwCast h = fp8_hw_cast(c);
+    const bool e4m3 = out_dtype == DT_FP8_143;
+    for (size_t i = 0; i < n; i++) {
+        const float x = bits_as_float(in[i]);
+        const float f = x * h.scale;
+        uint32_t fb;
+        memcpy(&fb, &f, 4);
+        const uint32_t fix = fp8_hw_fix(x, f, h);
+        const uint32_t hw = e4m3 ? f32_to_fp8(fb, 4, 7, RM_NE, 0, false, true, true, false, 2) : f32_to_fp8(fb, 5, 15, RM_NE, 0, false, true, true, false, 0);
+        out[i] = uint8_t(fix != 0x100u ? fix : hw);
+    }
+    return 0;
+}
 void hc_compare(const uint8_t* a, const uint8_t* b, uint8_t* equal, size_t n, int dtype, int bias, int mode, unsigned cd)
 {
     const CompareSpec c = make_compare_spec(dtype, bias, mode, cd);

@@ -102,6 +102,34 @@ def test_epilogue_flat_casts_equal_the_general_ones(hc):
                         assert (a == b).all(), (dt, bias, mode, rm, clip, cii, [hex(v) for v in bits[a != b][:5]], a[a != b][:5], b[a != b][:5])
 
 
+def test_hardware_fp8_path_constants(hc):
+    """The rescale, overflow thresholds and constant codes around the hardware fp8 conversion give the general cast's bits for
+    every 1-4-3 convention and the IEEE-like 1-5-2, every bias and clip flag (the hardware conversion itself is modelled on
+    the host as a saturating nearest-even cast into the hardware format; the GPU tests run the real instruction)."""
+    rng = np.random.default_rng(13)
+    ex = np.repeat(np.arange(256, dtype=np.uint32), 96)
+    dense = rng.integers(0, 2**23, ex.size).astype(np.uint32) | (ex << 23)
+    edges = np.concatenate([(ex << 23) + d for d in (0, 1, 0x7FFFFF, 0x400000, 0x3FFFFF, 0x400001, 0x100000, 0x080000, 0x0FFFFF, 0x700000, 0x780000,
+                                                      0x680000, 0x6FFFFF, 0x680001, 0x500000, 0x4FFFFF, 0x500001)]).astype(np.uint32)
+    special = np.array([0, 0x7F800000, 0x7FC00000, 0x7F800001, 0x7FFFFFFF], np.uint32)
+    bits = np.concatenate([dense, edges, special])
+    bits = np.concatenate([bits, bits | 0x80000000])
+    n = bits.size
+    zeros = np.zeros(n, np.uint32)
+    vp = lambda a: a.ctypes.data_as(C.c_void_p)  # noqa: E731
+    for dt, ew, biases, modes in ((abi.FP8_143, 4, (1, 3, 7, 11, 15), (0, 1, 2)), (abi.FP8_152, 5, (1, 15, 24, 31), (0,))):
+        for bias in biases:
+            for mode in modes:
+                for clip, cii in ((0, 0), (1, 0), (1, 1), (0, 1)):
+                    want, got = np.zeros(n, np.uint8), np.zeros(n, np.uint8)
+                    hc.hc_cast(vp(bits), vp(want), C.c_size_t(n), dt, ew, bias, mode, 0, 0, clip, cii, 0, 0, vp(zeros))
+                    assert hc.hc_cast_fp8_hw_model(vp(bits), vp(got), C.c_size_t(n), dt, ew, bias, mode, clip, cii) == 0
+                    bad = np.flatnonzero(want != got)
+                    assert bad.size == 0, (dt, bias, mode, clip, cii, [(hex(bits[i]), hex(want[i]), hex(got[i])) for i in bad[:6]])
+    # the conventions the hardware 1-5-2 format cannot express are not routed there
+    assert hc.hc_cast_fp8_hw_model(vp(bits), vp(got), C.c_size_t(n), abi.FP8_152, 5, 15, 2, 0, 0) == -1
+
+
 def test_foreign_code_predicate(hc, port):
     """A code is 'foreign' exactly when the reference decode differs from the tensor cores' decode
     (OCP E4M3 = the 1-4-3 'minimal' convention at bias 7; OCP E5M2 = the 1-5-2 'full' convention at bias 15)."""
