@@ -1677,7 +1677,7 @@ int mmeb200_memory_write(mmeb200_ctx* c, mmeb200_tensor* mem, const mmeb200_tens
         TRY(stage_in(c, mme_out, &so, true));
         TRY(stage_in(c, mem, &sm, true));
         if (n && mem->dtype == DT_FP32) {
-            memory_write_f32_kernel<<<grid_for((n + 3) / 4, 256, c->sm_count), 256, 0, c->stream>>>(static_cast<uint32_t*>(sm.t.data),
+            memory_write_f32_kernel<<<grid_for((n + 7) / 8, 256, c->sm_count), 256, 0, c->stream>>>(static_cast<uint32_t*>(sm.t.data),
                                                                                          static_cast<const uint32_t*>(so.t.data), n,
                                                                                          red_op, red_rm, clip_fp);
             c->launches++;

@@ -549,17 +549,33 @@ __device__ __forceinline__ uint32_t memory_write_f32_one(uint32_t a, uint32_t b,
     if (clip && f32_is_inf(r) && !f32_is_inf(a0) && !f32_is_inf(b0)) r -= 1;
     return r;
 }
-// 16 bytes of each tensor per thread and iteration (both are 16-byte aligned: arena or cudaMalloc), scalar tail.
+// Groups of four elements (16 bytes of each tensor; both are 16-byte aligned: arena or cudaMalloc). As in cast_kernel, a
+// warp takes kRmwGroups x 32 consecutive groups per iteration, lane l the groups l, l + 32, ...: contiguous accesses and
+// 2 x kRmwGroups loads in flight per thread. Scalar tail.
+constexpr int kRmwGroups = 2;
 __global__ void memory_write_f32_kernel(uint32_t* __restrict__ mem, const uint32_t* __restrict__ src, uint64_t n, int op, int rm,
                                         int clip) {
     const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
-    const uint64_t n4 = ((reinterpret_cast<uintptr_t>(mem) | reinterpret_cast<uintptr_t>(src)) & 15) ? 0 : n / 4;
-    for (uint64_t q = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; q < n4; q += stride) {
-        const uint4 a = reinterpret_cast<const uint4*>(mem)[q], b = reinterpret_cast<const uint4*>(src)[q];
-        reinterpret_cast<uint4*>(mem)[q] = make_uint4(memory_write_f32_one(a.x, b.x, op, rm, clip), memory_write_f32_one(a.y, b.y, op, rm, clip),
-                                                      memory_write_f32_one(a.z, b.z, op, rm, clip), memory_write_f32_one(a.w, b.w, op, rm, clip));
+    const uint64_t tid = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    constexpr uint64_t kChunk = kRmwGroups * 32;
+    const uint64_t chunks = ((reinterpret_cast<uintptr_t>(mem) | reinterpret_cast<uintptr_t>(src)) & 15) ? 0 : n / (4 * kChunk);
+    const uint32_t lane = threadIdx.x & 31;
+    for (uint64_t ch = tid >> 5; ch < chunks; ch += stride >> 5) {
+        uint4 a[kRmwGroups], b[kRmwGroups];
+#pragma unroll
+        for (int g = 0; g < kRmwGroups; ++g) {
+            const uint64_t q = ch * kChunk + g * 32 + lane;
+            a[g] = reinterpret_cast<const uint4*>(mem)[q];
+            b[g] = reinterpret_cast<const uint4*>(src)[q];
+        }
+#pragma unroll
+        for (int g = 0; g < kRmwGroups; ++g) {
+            const uint64_t q = ch * kChunk + g * 32 + lane;
+            reinterpret_cast<uint4*>(mem)[q] = make_uint4(memory_write_f32_one(a[g].x, b[g].x, op, rm, clip), memory_write_f32_one(a[g].y, b[g].y, op, rm, clip),
+                                                          memory_write_f32_one(a[g].z, b[g].z, op, rm, clip), memory_write_f32_one(a[g].w, b[g].w, op, rm, clip));
+        }
     }
-    for (uint64_t i = n4 * 4 + uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+    for (uint64_t i = chunks * kChunk * 4 + tid; i < n; i += stride)
         mem[i] = memory_write_f32_one(mem[i], src[i], op, rm, clip);
 }
 
