@@ -1682,7 +1682,7 @@ int mmeb200_memory_write(mmeb200_ctx* c, mmeb200_tensor* mem, const mmeb200_tens
                                                                                          red_op, red_rm, clip_fp);
             c->launches++;
         } else if (n) {
-            memory_write_bf16_kernel<<<grid_for(n, 256, c->sm_count), 256, 0, c->stream>>>(static_cast<uint16_t*>(sm.t.data),
+            memory_write_bf16_kernel<<<grid_for((n + 7) / 8, 256, c->sm_count), 256, 0, c->stream>>>(static_cast<uint16_t*>(sm.t.data),
                                                                                           static_cast<const uint16_t*>(so.t.data), n,
                                                                                           red_op, red_rm, clip_fp);
             c->launches++;

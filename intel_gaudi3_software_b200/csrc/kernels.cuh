@@ -580,9 +580,21 @@ __global__ void memory_write_f32_kernel(uint32_t* __restrict__ mem, const uint32
 }
 
 // The same reductions on bf16 tensors: 2 bytes read twice and written once per element.
+// Eight elements (16 bytes of each tensor) per thread and iteration when both bases are 16-byte aligned; scalar tail.
 __global__ void memory_write_bf16_kernel(uint16_t* __restrict__ mem, const uint16_t* __restrict__ src, uint64_t n, int op, int rm, int clip) {
     const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
-    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+    const uint64_t tid = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    const uint64_t n8 = ((reinterpret_cast<uintptr_t>(mem) | reinterpret_cast<uintptr_t>(src)) & 15) ? 0 : n / 8;
+    for (uint64_t q = tid; q < n8; q += stride) {
+        const uint4 a = reinterpret_cast<const uint4*>(mem)[q], b = reinterpret_cast<const uint4*>(src)[q];
+        const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
+        uint32_t r[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+            r[w] = bf16_rmw(wa[w] & 0xFFFFu, wb[w] & 0xFFFFu, op, rm, clip != 0) | (bf16_rmw(wa[w] >> 16, wb[w] >> 16, op, rm, clip != 0) << 16);
+        reinterpret_cast<uint4*>(mem)[q] = make_uint4(r[0], r[1], r[2], r[3]);
+    }
+    for (uint64_t i = n8 * 8 + tid; i < n; i += stride)
         mem[i] = uint16_t(bf16_rmw(mem[i], src[i], op, rm, clip != 0));
 }
 
