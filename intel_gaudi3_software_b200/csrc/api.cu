@@ -13,8 +13,8 @@
 #include <string>
 #include <vector>
 
+#include "gemm_launch.h"
 #include "gemm_sm100.cuh"
-#include "gemm_sm100_pair.cuh"
 #include "gaudi3_exact.cuh"
 #include "kernels.cuh"
 #include "mme_b200.h"
@@ -281,53 +281,13 @@ struct OutSpec {
     uint64_t seed, offset;
 };
 
-template <int KIND, int BLOCK_N, int STAGES>
-static int launch_gemm_kernel(mmeb200_ctx* c, const GemmParams& p, unsigned grid) {
-    auto kern = gemm_tcgen05_kernel<KIND, BLOCK_N, STAGES>;
-    constexpr int smem = GemmSmem<BLOCK_N, STAGES>::kTotal;
-    static bool configured[16] = {};
-    if (!configured[c->device & 15]) {
-        CUDA_OK(c, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        configured[c->device & 15] = true;
-    }
-    kern<<<grid, kGemmThreads, smem, c->stream>>>(p);
+static int launch_status(mmeb200_ctx* c, const LaunchResult& r) {
+    if (r.cuda != cudaSuccess) return c->fail(MMEB200_ERR_CUDA, "%s: %s", r.what, cudaGetErrorString(r.cuda));
+    if (r.code != LAUNCH_OK) return c->fail(MMEB200_ERR_CUDA, "%s", r.what);
     c->launches++;
-    CUDA_OK(c, cudaGetLastError());
     return 0;
 }
-
-// CTA-pair kernel: clusters of two CTAs; the grid is the number of pairs the device can hold at once (a cluster
-// needs both its SMs inside one GPC, so this can be fewer than sm_count / 2), or the tile count if that is smaller.
-template <int KIND, int EPI_GROUPS>
-static int launch_pair_kernel(mmeb200_ctx* c, const GemmParams& p, uint64_t tiles) {
-    auto kern = gemm_tcgen05_pair_kernel<KIND, EPI_GROUPS>;
-    constexpr int smem = PairSmem<EPI_GROUPS>::kTotal;
-    constexpr int threads = PairSmem<EPI_GROUPS>::kThreads;
-    static int max_pairs[16] = {};
-    int& cached = max_pairs[c->device & 15];
-    if (cached == 0) {
-        CUDA_OK(c, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        cudaLaunchConfig_t cfg;
-        memset(&cfg, 0, sizeof cfg);
-        cfg.gridDim = dim3(unsigned(c->sm_count) & ~1u);
-        cfg.blockDim = dim3(threads);
-        cfg.dynamicSmemBytes = smem;
-        cudaLaunchAttribute attr;
-        attr.id = cudaLaunchAttributeClusterDimension;
-        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
-        cfg.attrs = &attr;
-        cfg.numAttrs = 1;
-        int n = 0;
-        CUDA_OK(c, cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
-        if (n <= 0) return c->fail(MMEB200_ERR_CUDA, "no CTA pair fits on this device");
-        cached = n;
-    }
-    const unsigned pairs = unsigned(std::min<uint64_t>(tiles, uint64_t(cached)));
-    kern<<<pairs * 2, threads, smem, c->stream>>>(p);
-    c->launches++;
-    CUDA_OK(c, cudaGetLastError());
-    return 0;
-}
+static LaunchEnv launch_env(const mmeb200_ctx* c) { return LaunchEnv{c->device, c->sm_count, c->stream}; }
 
 struct GemmJob {
     TmaOperand a, b;
@@ -461,22 +421,9 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
         // ... and so does the general cast (stochastic rounding, fp8 output), hundreds of instructions per element
         bool two_groups = kb_per_tile <= 12 || (split == 1 && (p.epi_mode == EPI_GENERIC || p.epi_mode == EPI_FP8_HW));
         if (const char* e = getenv("MME_B200_EPI_GROUPS")) two_groups = atoi(e) == 2;            // tuning knob
-        if (two_groups)
-            rc = j.kind == KIND_F16 ? launch_pair_kernel<KIND_F16, 2>(c, p, pair_tiles)
-                 : j.kind == KIND_TF32 ? launch_pair_kernel<KIND_TF32, 2>(c, p, pair_tiles)
-                                       : launch_pair_kernel<KIND_F8, 2>(c, p, pair_tiles);
-        else
-            rc = j.kind == KIND_F16 ? launch_pair_kernel<KIND_F16, 1>(c, p, pair_tiles)
-                 : j.kind == KIND_TF32 ? launch_pair_kernel<KIND_TF32, 1>(c, p, pair_tiles)
-                                       : launch_pair_kernel<KIND_F8, 1>(c, p, pair_tiles);
-    } else if (block_n == 256) {
-        rc = j.kind == KIND_F16 ? launch_gemm_kernel<KIND_F16, 256, 4>(c, p, grid)
-             : j.kind == KIND_TF32 ? launch_gemm_kernel<KIND_TF32, 256, 4>(c, p, grid)
-                                   : launch_gemm_kernel<KIND_F8, 256, 4>(c, p, grid);
+        rc = launch_status(c, launch_gemm_pair(launch_env(c), j.kind, two_groups ? 2 : 1, p, pair_tiles));
     } else {
-        rc = j.kind == KIND_F16 ? launch_gemm_kernel<KIND_F16, 128, 6>(c, p, grid)
-             : j.kind == KIND_TF32 ? launch_gemm_kernel<KIND_TF32, 128, 6>(c, p, grid)
-                                   : launch_gemm_kernel<KIND_F8, 128, 6>(c, p, grid);
+        rc = launch_status(c, launch_gemm_single(launch_env(c), j.kind, block_n, p, grid));
     }
     TRY(rc);
     if (peer) {
@@ -1872,8 +1819,7 @@ extern "C" int mmeb200_gemm_splitk_static(mmeb200_ctx* c, mmeb200_tensor* out, c
     TRY(encode_tiled(c, &p.tm_b, b, b.mn_major ? kRowBytes / elem : block_k, b.mn_major ? block_k : block_n));
     const uint64_t tiles = uint64_t(p.m_tiles) * p.n_tiles * splits;
     const unsigned grid = unsigned(std::min<uint64_t>(tiles, uint64_t(c->sm_count)));
-    const int launch_rc = (kind == KIND_F16) ? launch_gemm_kernel<KIND_F16, 128, 6>(c, p, grid) : launch_gemm_kernel<KIND_F8, 128, 6>(c, p, grid);
-    TRY(launch_rc);
+    TRY(launch_status(c, launch_gemm_single(launch_env(c), kind, 128, p, grid)));
     ReduceOut r;
     memset(&r, 0, sizeof r);
     r.out = out->data; r.out_dtype = DT_FP32; r.has_cast = 0; r.out_ld = out->strides[1];

@@ -204,7 +204,7 @@ __device__ __forceinline__ void epilogue_general(uint32_t (&t)[32], const GemmPa
 // four elements needs the stream position aligned), else the general cast. One out-of-line copy serves every kernel and
 // both store paths; its argument lives in local memory, so the caller hands it a copy of the accumulator registers
 // (an array whose address is taken is in memory everywhere, the fast paths included).
-__device__ __noinline__ void epilogue_cast_any(uint32_t (&v)[32], const GemmParams& p, uint32_t out_elem, uint64_t flat_index) {
+static __device__ __noinline__ void epilogue_cast_any(uint32_t (&v)[32], const GemmParams& p, uint32_t out_elem, uint64_t flat_index) {
     const bool stream_ok = !p.rng_philox || ((p.rng_offset + flat_index) & 3u) == 0;
     if (stream_ok && dtype_is_fp8(p.cast.out_dtype) && !p.cast.ftz && !p.cast.sftz) {
         switch (p.cast.rm) {
