@@ -168,6 +168,16 @@ void mmeb200_destroy(mmeb200_ctx* ctx);
 enum { MMEB200_ACC_TENSOR_CORE = 0, MMEB200_ACC_CHIP_EXACT = 1 };
 int mmeb200_set_accumulation(mmeb200_ctx* ctx, int mode);
 
+/* Tuning knobs of a context; no counterpart in the reference (its calculator has limitNumOfThreads only). The planner
+ * picks tile shapes, K splits and store paths per problem; a knob forces one choice, value < 0 gives it back to the
+ * planner. Names: "pair" (0/1: CTA-pair kernel), "block_n" (128/256: single-CTA tile width), "split_k" (n > 0),
+ * "epi_groups" (1/2), "raster_gm" (m tiles per raster group), "tma_store" (0 = direct stores), "host_pipeline"
+ * (0 = host-tensor GEMMs staged whole), "stream_k" (0 = no split of the last wave of tiles). The same knobs take their
+ * defaults from environment variables read once in mmeb200_create (MME_B200_PAIR, MME_B200_BLOCK_N, MME_B200_SPLIT_K,
+ * MME_B200_EPI_GROUPS, MME_B200_GM, MME_B200_NO_TMA_STORE, MME_B200_NO_HOST_PIPELINE, MME_B200_STREAM_K); no launch
+ * reads the environment. Results do not depend on the knobs beyond the accumulation tolerance (summation order). */
+int mmeb200_set_option(mmeb200_ctx* ctx, const char* name, int value);
+
 /* Run all later work of this context on the caller's CUDA stream (a cudaStream_t passed as
  * void*); NULL goes back to the context's own stream. */
 int mmeb200_set_stream(mmeb200_ctx* ctx, void* cuda_stream);
@@ -234,6 +244,8 @@ int mmeb200_free(mmeb200_ctx* ctx, void* dev_ptr);
 int mmeb200_memcpy_h2d(mmeb200_ctx* ctx, void* dev_dst, const void* host_src, size_t bytes);
 int mmeb200_memcpy_d2h(mmeb200_ctx* ctx, void* host_dst, const void* dev_src, size_t bytes);
 int mmeb200_memset(mmeb200_ctx* ctx, void* dev_dst, int value, size_t bytes);
+/* Free and total device memory of the context's GPU (cudaMemGetInfo). */
+int mmeb200_mem_info(mmeb200_ctx* ctx, size_t* free_bytes, size_t* total_bytes);
 /* Pinned host staging memory, so host-tensor calls copy at full PCIe rate. */
 int mmeb200_host_alloc(void** host_ptr, size_t bytes);
 int mmeb200_host_free(void* host_ptr);
@@ -249,13 +261,16 @@ int mmeb200_timer_stop(mmeb200_ctx* ctx, float* elapsed_ms);
  * budget was fixed at start-up. out[M x N] (fp32) = op(x) . op(w) with the reduction cut into
  * `splits` parts whose fp32 partial sums live in a fixed 16 MiB array inside the library image
  * (held by every GPU that loads the library, until the process exits) instead of in scratch memory
- * from cudaMalloc. The call itself performs no cudaMalloc / cudaFree and calls no allocating routine.
+ * from cudaMalloc. After the first call on a device (see below) a call performs no cudaMalloc / cudaFree
+ * and calls no allocating routine: free device memory is the same before and after it.
  *   - tensors: device-resident, 2-D, 16-byte aligned, row pitches multiples of 16 bytes; bf16 x bf16,
  *     or fp8 whose Inf/NaN convention matches the tensor cores (1-4-3 minimal, 1-5-2 full);
  *   - limit: splits * M * N * 4 bytes <= 16 MiB, 2 <= splits <= 64; larger requests are rejected
  *     with MMEB200_ERR_INVALID_ARG and a message naming the limit;
- *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress) and
- *     should therefore come before any stream capture;
+ *   - the first call on a device does the one-time set-up: it looks up the array's device address
+ *     (cudaGetSymbolAddress), sets the kernel's shared-memory attribute, resolves the driver's
+ *     tensor-map encoder, and the CUDA runtime loads the kernels' module on first use. Make that
+ *     warm-up call where allocation is still allowed, and before any stream capture;
  *   - all calls share the one array and it keeps the previous call's partial sums. Each call
  *     overwrites every element it later reads, so nothing needs clearing, but two calls that
  *     overlap on the GPU (different streams or contexts) race on it: serialise them. */

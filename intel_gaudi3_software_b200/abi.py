@@ -141,6 +141,7 @@ P = C.POINTER
 SYMBOLS = {
     "mmeb200_create": (C.c_int, [P(C.c_void_p), C.c_int, C.c_int, C.c_uint, C.c_uint32, P(C.c_uint32), C.c_uint32]),
     "mmeb200_destroy": (None, [C.c_void_p]),
+    "mmeb200_set_option": (C.c_int, [C.c_void_p, C.c_char_p, C.c_int]),
     "mmeb200_set_stream": (C.c_int, [C.c_void_p, C.c_void_p]),
     "mmeb200_limit_num_of_threads": (C.c_int, [C.c_void_p, C.c_uint]),
     "mmeb200_bgemm": (C.c_int, [C.c_void_p, P(Tensor), P(Tensor), P(Tensor), C.c_int, P(CastParams)]),
@@ -160,6 +161,7 @@ SYMBOLS = {
     "mmeb200_memcpy_h2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
     "mmeb200_memcpy_d2h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
     "mmeb200_memset": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_size_t]),
+    "mmeb200_mem_info": (C.c_int, [C.c_void_p, P(C.c_size_t), P(C.c_size_t)]),
     "mmeb200_host_alloc": (C.c_int, [P(C.c_void_p), C.c_size_t]),
     "mmeb200_host_free": (C.c_int, [C.c_void_p]),
     "mmeb200_timer_start": (C.c_int, [C.c_void_p]),

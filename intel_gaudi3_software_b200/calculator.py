@@ -152,6 +152,10 @@ class Calculator:
         arr = np.ascontiguousarray(regs, dtype=np.uint32)
         self._check(self.lib.mmeb200_set_lfsr(self.ctx, arr.ctypes.data_as(C.POINTER(C.c_uint32)), arr.size, polynomial))
 
+    def set_option(self, name, value):
+        """Force one of the planner's choices (include/mme_b200.h: mmeb200_set_option); value < 0 = automatic."""
+        self._check(self.lib.mmeb200_set_option(self.ctx, name.encode(), int(value)))
+
     def set_stream(self, cuda_stream_handle):
         self._check(self.lib.mmeb200_set_stream(self.ctx, cuda_stream_handle))
 
@@ -172,6 +176,12 @@ class Calculator:
         ms = C.c_float()
         self._check(self.lib.mmeb200_timer_stop(self.ctx, C.byref(ms)))
         return ms.value
+
+    def mem_info(self):
+        """(free, total) bytes of device memory on the calculator's GPU."""
+        free, total = C.c_size_t(), C.c_size_t()
+        self._check(self.lib.mmeb200_mem_info(self.ctx, C.byref(free), C.byref(total)))
+        return free.value, total.value
 
     def launch_count(self):
         return int(self.lib.mmeb200_launch_count(self.ctx))

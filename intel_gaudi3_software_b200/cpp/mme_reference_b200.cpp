@@ -6,12 +6,13 @@
 // reference's sim_tensor*.cpp in place of mme_reference_impl.cpp; callers do not change.
 //
 // Semantics kept from the reference:
-//   - doBatchGemm and dedx write into the output tensor's buffer in place; fwd / dedw / transposes
-//     give the output tensor a fresh buffer (mme_reference_impl.cpp:862-868, 396-428);
+//   - doBatchGemm, dedx and transposed_dedx write into the output tensor's buffer in place, through its
+//     strides (col2im, mme_reference_impl.cpp:858-861); fwd / dedw / the doDma transposes give the output
+//     tensor a fresh buffer (mme_reference_impl.cpp:862-868, 396-428);
 //   - failures surface as MME_ASSERT (mme/include/mme_assert.h:27-60);
 //   - one calculator = one host thread at a time.
 // Not available on this backend (asserts): integer / gemmlowp paths (zeroPoints, ActivationParams),
-// fp16 / ufp16 operands, transposed_dedx.
+// fp16 / ufp16 operands.
 #include <cstring>
 #include <string>
 
@@ -237,9 +238,10 @@ void CPUCalculator::doConvolution(MmeSimTensor& outputTensor, const MmeSimTensor
     p.padding_value = params.paddingValue.int32;
     p.relu = params.relu;
     mmeb200_tensor x = describe(xTensor, xTensor.data()), w = describe(wTensor, wTensor.data()), y = describe(yTensor, yTensor.data());
-    if (op == e_mme_dedx)
+    if (op == e_mme_dedx || op == e_mme_transposed_dedx)
     {
-        // written in place through the tensor's strides (RefIm2Col::doCol2Im)
+        // both end in RefIm2Col::doCol2Im, which writes in place through the tensor's strides: a caller-owned
+        // (non-owning) buffer receives the result and the gaps of a strided tensor keep their contents
         mmeb200_tensor o = describe(outputTensor, outputTensor.data());
         m_impl->check(mmeb200_conv(m_impl->ctx, &o, &x, &w, &y, &p, (int) op, (int) rm, nullptr));
         return;

@@ -4,6 +4,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <vector>
 
 #include "mme_reference.h"
 #include "data_types/non_standard_dtypes.h"
@@ -213,6 +214,51 @@ static void fill_and_compare()
     }
 }
 
+// transposed_dedx (mme_reference_impl.cpp:625-647): weights arrive as [C, K, S, R]; the calculator swaps the two fastest
+// dims, mirrors S and runs dedx, whose col2im writes IN PLACE. Checked: the result lands in a caller-owned buffer that the
+// output tensor does not own, and equals dedx on weights prepared by hand the same way.
+static void transposed_dedx_in_place()
+{
+    const unsigned C = 8, K = 16, W = 6, H = 5, B = 2, S = 3, R = 3;
+    SizeArray xs = {C, W, H, B, 1}, ws = {K, C, S, R, 1}, wts = {C, K, S, R, 1}, ys = {K, W, H, B, 1};
+    const unsigned nx = C * W * H * B, nw = K * C * S * R, ny = K * W * H * B;
+    MmeSimTensor w(ws, 4, e_type_bf16), wt(wts, 4, e_type_bf16), y(ys, 4, e_type_bf16);
+    std::vector<uint16_t> wv(nw), wtv(nw), yv(ny);
+    unsigned seed = 12345;
+    auto next = [&]() { seed = seed * 1664525u + 1013904223u; return float(int((seed >> 20) & 15) - 8) * 0.25f; };
+    for (auto& v : yv) v = (uint16_t) bf16_t(next(), RoundingMode::RoundToNearest);
+    // w[k, c, s, r] (K fastest) drawn at random; wt[c, k, s', r] = w[k, c, S-1-s', r]
+    for (unsigned i = 0; i < nw; i++) wv[i] = (uint16_t) bf16_t(next(), RoundingMode::RoundToNearest);
+    for (unsigned r = 0; r < R; r++)
+        for (unsigned s = 0; s < S; s++)
+            for (unsigned c = 0; c < C; c++)
+                for (unsigned k = 0; k < K; k++)
+                    wtv[((r * S + (S - 1 - s)) * K + k) * C + c] = wv[((r * S + s) * C + c) * K + k];
+    std::memcpy(w.data(), wv.data(), nw * 2);
+    std::memcpy(wt.data(), wtv.data(), nw * 2);
+    std::memcpy(y.data(), yv.data(), ny * 2);
+    ConvolutionParams params;
+    params.dim = 2;
+    params.padding[0] = params.padding[1] = 1;
+    CPUCalculator calculator(e_mme_Gaudi3);
+    MmeSimTensor dx(xs, 4, e_type_fp32);
+    calculator.doConvolution(dx, dx, w, y, params, e_mme_dedx, RoundingMode::RoundToNearest);
+    // the caller's buffer, handed over without ownership and pre-filled with a marker
+    std::vector<float> mine(nx, -77.0f);
+    MmeSimTensor dxt(xs, 4, e_type_fp32, (char*) mine.data());
+    EXPECT(dxt.data() == (char*) mine.data());
+    calculator.doConvolution(dxt, dxt, wt, y, params, e_mme_transposed_dedx, RoundingMode::RoundToNearest);
+    EXPECT(dxt.data() == (char*) mine.data());   // still the caller's buffer: no fresh allocation was swapped in
+    unsigned diff = 0, nonzero = 0;
+    for (unsigned i = 0; i < nx; i++)
+    {
+        diff += mine[i] != ((float*) dx.data())[i];
+        nonzero += mine[i] != 0.0f;
+    }
+    EXPECT(diff == 0);
+    EXPECT(nonzero > nx / 2);
+}
+
 int main()
 {
     gemm_simple_fp32();
@@ -227,6 +273,7 @@ int main()
     gemm_api_bf16_transposed();
     unsupported_type_asserts();
     fill_and_compare();
+    transposed_dedx_in_place();
     std::printf(g_failures ? "shim unit tests: %d FAILED\n" : "shim unit tests: all passed\n", g_failures);
     return g_failures ? 1 : 0;
 }

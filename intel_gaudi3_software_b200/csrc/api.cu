@@ -27,8 +27,27 @@ struct ArenaBlock {
     size_t size, used;
 };
 
+// Tuning knobs of a context (-1 = let the planner decide). Their defaults come from the environment ONCE, when the
+// context is created (MME_B200_PAIR, _BLOCK_N, _SPLIT_K, _EPI_GROUPS, _GM, _NO_TMA_STORE, _NO_HOST_PIPELINE, _STREAM_K);
+// mmeb200_set_option changes them per context afterwards. No launch reads the environment.
+struct Tuning {
+    int pair = -1;            // 0 / 1: CTA-pair kernel off / on where it applies
+    int block_n = -1;         // 128 / 256: single-CTA tile width (turns the pair kernel off)
+    int split_k = -1;         // > 0: forced number of K splits
+    int epi_groups = -1;      // 1 / 2: groups of four epilogue warps in the pair kernel
+    int raster_gm = -1;       // m tiles per raster group
+    int tma_store = -1;       // 0: direct stores even where a TMA store applies
+    int host_pipeline = -1;   // 0: host-tensor GEMMs are staged whole instead of pipelined
+    int stream_k = -1;        // 0: no tail split of the last wave
+};
+static int env_int(const char* name, int dflt) {
+    const char* e = getenv(name);
+    return e ? atoi(e) : dflt;
+}
+
 struct mmeb200_ctx {
     int device = 0, chip = 2, sm_count = 148;
+    Tuning tune;
     unsigned seed = 0;
     cudaStream_t own_stream = nullptr, stream = nullptr;
     std::string err;
@@ -323,11 +342,12 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     // Tile geometry. CTA pairs (one 256 x 256 tile per two SMs, half the B traffic per SM) whenever the
     // problem is at least one such tile; else 128 x 256 tiles per CTA whenever N has the columns; else
     // 128 x 128. Split-K below fills the machine when that leaves few tiles.
+    const Tuning& tune = c->tune;
     bool use_pair = j.M >= 256 && j.N >= 256;
-    if (const char* e = getenv("MME_B200_PAIR")) use_pair = use_pair && atoi(e) != 0;            // tuning knob
+    if (tune.pair >= 0) use_pair = use_pair && tune.pair != 0;
     const bool wide = j.N > 128;
     int block_n = wide ? 256 : 128;
-    if (const char* e = getenv("MME_B200_BLOCK_N")) { block_n = atoi(e) == 256 ? 256 : 128; use_pair = false; }   // tuning knob
+    if (tune.block_n >= 0) { block_n = tune.block_n == 256 ? 256 : 128; use_pair = false; }
     uint64_t tiles, units;   // units = CTAs or CTA pairs the device runs at once
     if (use_pair) {
         p.m_tiles = (j.M + 255) / 256;
@@ -339,10 +359,10 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
         units = uint64_t(c->sm_count);
     }
     p.raster_gm = 16;
-    if (const char* e = getenv("MME_B200_GM")) p.raster_gm = std::max(1, atoi(e));               // tuning knob
+    if (tune.raster_gm > 0) p.raster_gm = tune.raster_gm;
     tiles = uint64_t(p.m_tiles) * p.n_tiles * p.batches;
     uint32_t split = 1;
-    if (const char* e = getenv("MME_B200_SPLIT_K")) j.force_split = atoi(e);                   // tuning knob
+    if (tune.split_k > 0) j.force_split = tune.split_k;
     if (j.force_split > 0) split = std::min<uint32_t>(j.force_split, p.num_k_blocks);
     else if (tiles * 2 <= units && p.num_k_blocks >= 32) {
         // worth it only when the k loop is long: the partial sums cost a second kernel and (splits + 1) passes over M x N floats
@@ -353,7 +373,7 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     while (split > 1 && ((p.num_k_blocks + split - 1) / split) * (split - 1) >= p.num_k_blocks) --split;
     // A small problem that is not split and would leave most SMs idle runs as 128 x 128 tiles: half the work per SM
     // on up to four times as many SMs (1024^3 bf16: 11.5 us instead of 14.4 us).
-    if (split == 1 && !getenv("MME_B200_BLOCK_N") && !getenv("MME_B200_PAIR")) {
+    if (split == 1 && tune.block_n < 0 && tune.pair < 0) {
         const uint64_t sms_used = use_pair ? tiles * 2 : tiles;
         const uint64_t t128 = uint64_t((j.M + 127) / 128) * ((j.N + 127) / 128) * p.batches;
         if (sms_used * 2 <= uint64_t(c->sm_count) && t128 <= uint64_t(c->sm_count) && t128 > sms_used) {
@@ -405,7 +425,7 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     if (!j.b.mn_major) TRY(encode_tiled(c, &p.tm_b, j.b, p.block_k, block_n));
     else TRY(encode_tiled(c, &p.tm_b, j.b, kRowBytes / elem, p.block_k));
     // coalesced TMA stores when the output's base and pitches allow a tensor map
-    if (split == 1 && !peer && !getenv("MME_B200_NO_TMA_STORE")) {
+    if (split == 1 && !peer && tune.tma_store != 0) {
         TmaOperand od;
         od.ptr = o.ptr; od.elem = dtype_size(o.dtype); od.mn_major = false; od.inner = j.N; od.rows = j.M; od.row_stride = o.ld;
         for (int i = 0; i < 3; ++i) { od.bsz[i] = j.bsz[i]; od.bstride[i] = o.bstride[i]; }
@@ -420,7 +440,7 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
         const uint32_t kb_per_tile = (p.num_k_blocks + split - 1) / split;
         // ... and so does the general cast (stochastic rounding, fp8 output), hundreds of instructions per element
         bool two_groups = kb_per_tile <= 12 || (split == 1 && (p.epi_mode == EPI_GENERIC || p.epi_mode == EPI_FP8_HW));
-        if (const char* e = getenv("MME_B200_EPI_GROUPS")) two_groups = atoi(e) == 2;            // tuning knob
+        if (tune.epi_groups > 0) two_groups = tune.epi_groups == 2;
         rc = launch_status(c, launch_gemm_pair(launch_env(c), j.kind, two_groups ? 2 : 1, p, pair_tiles));
     } else {
         rc = launch_status(c, launch_gemm_single(launch_env(c), j.kind, block_n, p, grid));
@@ -814,9 +834,9 @@ static int bgemm_core(mmeb200_ctx* c, const mmeb200_tensor* out, const mmeb200_t
 // Host-tensor GEMMs large enough for the PCIe copies to dominate are run as a pipeline: B is
 // uploaded once, then A arrives in row blocks; block i is multiplied while block i+1 uploads and
 // block i-1's output downloads (PCIe is full duplex, the copies of the two directions overlap).
-static bool host_pipeline_applies(const mmeb200_tensor* out, const mmeb200_tensor* x, const mmeb200_tensor* w, int op,
+static bool host_pipeline_applies(const mmeb200_ctx* c, const mmeb200_tensor* out, const mmeb200_tensor* x, const mmeb200_tensor* w, int op,
                                   const mmeb200_cast_params* cast, uint64_t M, uint64_t N, uint64_t K) {
-    if (getenv("MME_B200_NO_HOST_PIPELINE")) return false;
+    if (c->tune.host_pipeline == 0) return false;
     if (out->mem_space != MMEB200_MEM_HOST || x->mem_space != MMEB200_MEM_HOST || w->mem_space != MMEB200_MEM_HOST) return false;
     if (op != MMEB200_OP_AB && op != MMEB200_OP_ABT) return false;  // rows of x must be rows of the product
     for (int d = 2; d < 5; ++d)
@@ -909,6 +929,14 @@ int mmeb200_create(mmeb200_ctx** out_ctx, int chip, int device, unsigned seed, u
     if (cudaSetDevice(device) != cudaSuccess) return MMEB200_ERR_CUDA;
     mmeb200_ctx* c = new mmeb200_ctx();
     c->device = device; c->chip = chip; c->seed = seed; c->sm_count = prop.multiProcessorCount;
+    c->tune.pair = env_int("MME_B200_PAIR", -1);
+    c->tune.block_n = env_int("MME_B200_BLOCK_N", -1);
+    c->tune.split_k = env_int("MME_B200_SPLIT_K", -1);
+    c->tune.epi_groups = env_int("MME_B200_EPI_GROUPS", -1);
+    c->tune.raster_gm = env_int("MME_B200_GM", -1);
+    c->tune.tma_store = getenv("MME_B200_NO_TMA_STORE") ? 0 : -1;
+    c->tune.host_pipeline = getenv("MME_B200_NO_HOST_PIPELINE") ? 0 : -1;
+    c->tune.stream_k = env_int("MME_B200_STREAM_K", -1);
     if (cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) != cudaSuccess || cudaMalloc(&c->d_status, 64) != cudaSuccess ||
         cudaMallocHost(&c->h_status, 64) != cudaSuccess || cudaEventCreate(&c->ev0) != cudaSuccess || cudaEventCreate(&c->ev1) != cudaSuccess) {
         delete c;
@@ -963,6 +991,20 @@ int mmeb200_set_accumulation(mmeb200_ctx* c, int mode) {
         return c->fail(MMEB200_ERR_UNSUPPORTED, "bit-exact accumulation is implemented for the Gaudi3 model only");
     c->acc_mode = mode;
     return 0;
+}
+
+int mmeb200_set_option(mmeb200_ctx* c, const char* name, int value) {
+    if (!c || !name) return MMEB200_ERR_INVALID_ARG;
+    struct { const char* name; int Tuning::*field; } const table[] = {
+        {"pair", &Tuning::pair}, {"block_n", &Tuning::block_n}, {"split_k", &Tuning::split_k}, {"epi_groups", &Tuning::epi_groups},
+        {"raster_gm", &Tuning::raster_gm}, {"tma_store", &Tuning::tma_store}, {"host_pipeline", &Tuning::host_pipeline},
+        {"stream_k", &Tuning::stream_k}};
+    for (const auto& t : table)
+        if (strcmp(t.name, name) == 0) {
+            c->tune.*(t.field) = value < 0 ? -1 : value;
+            return 0;
+        }
+    return c->fail(MMEB200_ERR_INVALID_ARG, "unknown option '%s'", name);
 }
 
 int mmeb200_set_stream(mmeb200_ctx* c, void* s) {
@@ -1022,6 +1064,12 @@ int mmeb200_memset(mmeb200_ctx* c, void* d, int value, size_t bytes) {
     if (!c) return MMEB200_ERR_INVALID_ARG;
     cudaSetDevice(c->device);
     CUDA_OK(c, cudaMemsetAsync(d, value, bytes, c->stream));
+    return 0;
+}
+int mmeb200_mem_info(mmeb200_ctx* c, size_t* free_bytes, size_t* total_bytes) {
+    if (!c || !free_bytes || !total_bytes) return MMEB200_ERR_INVALID_ARG;
+    cudaSetDevice(c->device);
+    CUDA_OK(c, cudaMemGetInfo(free_bytes, total_bytes));
     return 0;
 }
 int mmeb200_host_alloc(void** p, size_t bytes) {
@@ -1091,7 +1139,7 @@ int mmeb200_bgemm(mmeb200_ctx* c, mmeb200_tensor* out, const mmeb200_tensor* x, 
     }
     if (K != Kb) return c->fail(MMEB200_ERR_INVALID_ARG, "Common dim doesnt match between input A\\B");
     if (out->sizes[0] != N || out->sizes[1] != M) return c->fail(MMEB200_ERR_INVALID_ARG, "output width doesnt match to inputB width");
-    if (host_pipeline_applies(out, x, w, op, cast, M, N, K)) return bgemm_host_pipelined(c, out, x, w, op, cast, M, N, K);
+    if (host_pipeline_applies(c, out, x, w, op, cast, M, N, K)) return bgemm_host_pipelined(c, out, x, w, op, cast, M, N, K);
     TRY(stage_in(c, x, &sx, true));
     TRY(stage_in(c, w, &sw, true));
     TRY(stage_in(c, out, &so, !is_dense(out)));

@@ -13,10 +13,18 @@ REF_SO = os.path.join(HERE, "_ref", "libmme_ref.so")
 P = C.POINTER
 
 
-def build(ref_root="/root/reference"):
+def reference_root():
+    """Where the reference's checkout lies: $MME_REFERENCE_ROOT, else a directory `reference` beside this repository.
+    Returns None when there is none (the GPU box: only the prebuilt checkers travel there)."""
+    root = os.environ.get("MME_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return root if os.path.exists(os.path.join(root, "mme", "mme_reference", "mme_reference.h")) else None
+
+
+def build(ref_root=None):
     """Compile the C restatement, and the reference itself when its checkout is present."""
     subprocess.check_call(["make", "-s", "-C", HERE, "port"])
-    if os.path.exists(os.path.join(ref_root, "mme", "mme_reference", "mme_reference.h")):
+    ref_root = ref_root or reference_root()
+    if ref_root and os.path.exists(os.path.join(ref_root, "mme", "mme_reference", "mme_reference.h")):
         subprocess.check_call(["make", "-s", "-j8", "-C", HERE, "ref", "REF=" + ref_root])
 
 

@@ -1,9 +1,8 @@
 """The benchmark's vectorised fp8 quantiser produces the same code bytes as the reference's RNE cast
-(so bench inputs are what BASELINE config 2 describes: N(0,1) scaled to amax = max finite, RNE)."""
+(so the fp8 GEMM inputs are what the configuration describes: N(0,1) scaled to amax = max finite, RNE)."""
 import numpy as np
 
-import bench
-from intel_gaudi3_software_b200 import abi
+from intel_gaudi3_software_b200 import abi, workloads as bench
 
 
 def test_quantiser_matches_oracle(port):
@@ -17,7 +16,7 @@ def test_quantiser_matches_oracle(port):
         assert (got == want).all(), (dtype, int((got != want).sum()))
 
 
-def test_workload_counts_match_baseline_table():
+def test_workload_counts_match_the_configurations():
     f, b = bench.workload_counts(bench.WORKLOADS["fp8_gemm_8192"])
     assert f == 2.0 * 8192**3 and b == 2 * 8192 * 8192 + 2 * 8192 * 8192
     f, b = bench.workload_counts(bench.WORKLOADS["conv_fwd"])

@@ -86,10 +86,12 @@ def test_errors():
         p.parse({"nothing": []})
 
 
-REF_CONFIGS = "/root/reference/mme/mme_verification"
+from oracle.oracle import reference_root  # noqa: E402
+
+REF_CONFIGS = os.path.join(reference_root() or "", "mme", "mme_verification")
 
 
-@pytest.mark.skipif(not os.path.isdir(REF_CONFIGS), reason="no checkout of the reference here")
+@pytest.mark.skipif(reference_root() is None, reason="no checkout of the reference here")
 def test_reference_corpus_parses():
     """Every config of the reference's corpus is read; tests on fp16 operands are counted as rejected,
     everything else must parse into runnable test descriptions."""

@@ -55,24 +55,30 @@ def test_shapes(calc, best_oracle, M, N, K):
 
 
 KERNEL_VARIANTS = {
-    "pair, four epilogue warps": {"MME_B200_PAIR": "1", "MME_B200_EPI_GROUPS": "1"},
-    "pair, eight epilogue warps": {"MME_B200_PAIR": "1", "MME_B200_EPI_GROUPS": "2"},
-    "pair, split-K": {"MME_B200_PAIR": "1", "MME_B200_SPLIT_K": "3"},
-    "single CTA, 256 wide": {"MME_B200_PAIR": "0"},
-    "single CTA, 128 wide": {"MME_B200_BLOCK_N": "128"},
-    "single CTA, no TMA stores": {"MME_B200_PAIR": "0", "MME_B200_NO_TMA_STORE": "1"},
+    "pair, four epilogue warps": {"pair": 1, "epi_groups": 1},
+    "pair, eight epilogue warps": {"pair": 1, "epi_groups": 2},
+    "pair, split-K": {"pair": 1, "split_k": 3},
+    "pair, no split of the last wave": {"pair": 1, "stream_k": 0},
+    "single CTA, 256 wide": {"pair": 0},
+    "single CTA, 128 wide": {"block_n": 128},
+    "single CTA, no TMA stores": {"pair": 0, "tma_store": 0},
 }
 
 
 @pytest.mark.parametrize("variant", sorted(KERNEL_VARIANTS))
-def test_every_kernel_variant_matches_the_oracle(calc, best_oracle, variant, monkeypatch):
-    """The tile geometry is picked per problem; the tuning knobs force each form on the same problems."""
-    for k, v in KERNEL_VARIANTS[variant].items():
-        monkeypatch.setenv(k, v)   # the library reads its knobs per call
-    run_case(calc, best_oracle, 512, 768, 520, abi.OP_AB, seed=3)
-    run_case(calc, best_oracle, 300, 260, 200, abi.OP_ABT, seed=4)
-    run_case(calc, best_oracle, 256, 256, 96, abi.OP_ATB, batch=(3, 2), w_batch=(1, 2), seed=5)
-    run_case(calc, best_oracle, 384, 520, 72, abi.OP_ATBT, o_pitch=8, seed=6)
+def test_every_kernel_variant_matches_the_oracle(calc, best_oracle, variant):
+    """The tile geometry is picked per problem; the context's tuning knobs force each form on the same problems."""
+    knobs = KERNEL_VARIANTS[variant]
+    try:
+        for k, v in knobs.items():
+            calc.set_option(k, v)
+        run_case(calc, best_oracle, 512, 768, 520, abi.OP_AB, seed=3)
+        run_case(calc, best_oracle, 300, 260, 200, abi.OP_ABT, seed=4)
+        run_case(calc, best_oracle, 256, 256, 96, abi.OP_ATB, batch=(3, 2), w_batch=(1, 2), seed=5)
+        run_case(calc, best_oracle, 384, 520, 72, abi.OP_ATBT, o_pitch=8, seed=6)
+    finally:
+        for k in knobs:
+            calc.set_option(k, -1)
 
 
 @pytest.mark.parametrize("op", [abi.OP_AB, abi.OP_ABT, abi.OP_ATB, abi.OP_ATBT])
@@ -161,7 +167,7 @@ def test_fp8_all_formats_biases_and_infnan_modes(calc, best_oracle, port, tx, tw
 
 def test_fp8_same_type_is_bit_identical_to_the_reference_model(calc, best_oracle, port):
     """fp8 x fp8 products are exact in fp32 and short sums stay exact: for in-range values the
-    tensor-core accumulation and the reference's tree agree bit for bit at K = 128 (BASELINE config 5a)."""
+    tensor-core accumulation and the reference's tree agree bit for bit at K = 128 (the attention-shaped batch)."""
     rng = np.random.default_rng(8)
     M, N, K = 128, 256, 128
     xb, wb = util.gen_fp8(rng, M * K, port), util.gen_fp8(rng, K * N, port)

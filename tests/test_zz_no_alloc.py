@@ -7,9 +7,11 @@ device-memory budget was fixed when it started. The entry point keeps the fp32 p
 split reduction in a fixed 16 MiB array that is part of the library image, and calls no allocator.
 
 The test calls it through the C ABI on device-resident tensors and compares with the ordinary entry
-point (mmeb200_bgemm) on the same inputs, twice in a row with different shapes, so that partial sums
-left behind by the first call would show up in the second. This file sorts last on purpose: a run
-that stops at the first failure has then already run every other test.
+point (mmeb200_bgemm) and with the CPU oracle on the same inputs, twice in a row with different shapes,
+so that partial sums left behind by the first call would show up in the second. It also checks the
+property the entry point exists for: after a warm-up call (the one-time set-up) free device memory is
+the same before and after a call. This file sorts last on purpose: a run that stops at the first
+failure has then already run every other test.
 """
 import numpy as np
 import pytest
@@ -22,7 +24,7 @@ import util
 pytestmark = pytest.mark.gpu
 
 
-def run_both(calc, rng, M, N, K, op, splits, dtype=abi.BF16):
+def run_both(calc, rng, M, N, K, op, splits, dtype=abi.BF16, oracle=None, port=None):
     tA, tB = op in (abi.OP_ATB, abi.OP_ATBT), op in (abi.OP_ABT, abi.OP_ATBT)
     xs = [M, K] if tA else [K, M]
     ws = [K, N] if tB else [N, K]
@@ -39,7 +41,11 @@ def run_both(calc, rng, M, N, K, op, splits, dtype=abi.BF16):
     d_static, d_plain = calc.alloc(M * N * 4), calc.alloc(M * N * 4)
     x = T(dx.ptr, dtype, xs, mem_space=abi.MEM_DEVICE, **kw)
     w = T(dw.ptr, dtype, ws, mem_space=abi.MEM_DEVICE, **kw)
+    calc.sync()
+    free_before = calc.mem_info()[0]
     calc.gemm_splitk_static(T(d_static.ptr, abi.FP32, [N, M], mem_space=abi.MEM_DEVICE), x, w, op, splits)
+    calc.sync()
+    free_after = calc.mem_info()[0]
     calc.do_batch_gemm(T(d_plain.ptr, abi.FP32, [N, M], mem_space=abi.MEM_DEVICE), x, w, op)
     calc.sync(10_000_000_000)
     a, b = d_static.download(np.float32), d_plain.download(np.float32)
@@ -47,17 +53,27 @@ def run_both(calc, rng, M, N, K, op, splits, dtype=abi.BF16):
         buf.free()
     # same products, different summation order: the accumulator tolerance of the other GPU tests
     assert np.abs(a.astype(np.float64) - b.astype(np.float64)).max() <= util.ACC_TOL * bound, (M, N, K, op, splits)
-    return a
+    if oracle is not None:
+        # against the CPU oracle, per element: |gpu - ref| <= 1e-5 * sum|a_k b_k|
+        ref = np.zeros(M * N, np.float32)
+        assert oracle.bgemm(T(ref, abi.FP32, [N, M]), T(xb, dtype, xs, **kw), T(wb, dtype, ws, **kw), op) == 0
+        xf = util.decode(xb, dtype, 7, 2, port).reshape(xs[::-1])
+        wf = util.decode(wb, dtype, 7, 2, port).reshape(ws[::-1])
+        sabs = util.sum_abs_products(xf.T if tA else xf, wf.T if tB else wf)
+        util.assert_acc(a, ref, sabs, "allocation-free gemm %dx%dx%d" % (M, N, K))
+    return a, free_before, free_after
 
 
-def test_two_calls_in_a_row_match_the_ordinary_entry_point():
+def test_two_calls_in_a_row_match_the_ordinary_entry_point(best_oracle, port):
     calc = pkg.Calculator(device=0)
     rng = np.random.default_rng(2024)
-    first = run_both(calc, rng, 256, 384, 2048, abi.OP_AB, 4)
+    first, _, _ = run_both(calc, rng, 256, 384, 2048, abi.OP_AB, 4, oracle=best_oracle, port=port)
     # second call: smaller output, more splits, other orientation -- reads only what it wrote itself
-    second = run_both(calc, rng, 100, 72, 4096, abi.OP_ABT, 16)
+    second, before, after = run_both(calc, rng, 100, 72, 4096, abi.OP_ABT, 16, oracle=best_oracle, port=port)
     assert np.isfinite(first).all() and np.isfinite(second).all()
-    run_both(calc, rng, 128, 128, 1024, abi.OP_AB, 8, dtype=abi.FP8_143)
+    # the first call was the warm-up (one-time set-up); from then on a call leaves free device memory as it found it
+    assert before == after, (before, after)
+    _, before, after = run_both(calc, rng, 128, 128, 1024, abi.OP_AB, 8, dtype=abi.FP8_143, oracle=best_oracle, port=port)
     calc.close()
 
 

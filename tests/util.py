@@ -11,20 +11,13 @@ Tolerances (stated here once, used by every accumulation test):
 """
 import numpy as np
 
-from intel_gaudi3_software_b200 import abi
+from intel_gaudi3_software_b200 import abi, workloads
 
 ACC_TOL = 1e-5
 
 
-def bf16_to_f32(u16):
-    return (np.asarray(u16, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
-
-
-def f32_to_bf16_rne(x):
-    """Round-to-nearest-even fp32 -> bf16 bit patterns (finite inputs; same result as fp32_to_bf16 RNE)."""
-    b = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
-    r = ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
-    return r
+bf16_to_f32 = workloads.bf16_to_f32
+f32_to_bf16_rne = workloads.f32_to_bf16_rne
 
 
 def decode(arr, dtype, bias=0, mode=0, oracle=None):
@@ -42,7 +35,7 @@ def gen_bf16(rng, n, dist="uniform", scale=1.0):
 
 
 def gen_fp8(rng, n, oracle, dtype=abi.FP8_143, bias=7, mode=abi.INFNAN_MINIMAL, amax_target=None):
-    """N(0,1) scaled so that amax lands on the format's largest finite value, RNE-cast (BASELINE config 2)."""
+    """N(0,1) scaled so that amax lands on the format's largest finite value, RNE-cast (the fp8 8192^3 GEMM configuration)."""
     v = rng.normal(0, 1, n).astype(np.float32)
     ew = 4 if dtype == abi.FP8_143 else 5
     if amax_target is None:
@@ -92,3 +85,31 @@ def check_rounded(gpu_bits, ref_bits, width, gpu_val, ref_val, sabs, name=""):
         assert not bad.any(), "%s: %d outputs differ by more than 1 ulp and more than the accumulator tolerance" % (
             name, int(bad.sum()))
     return inexact, int(far.sum())
+
+
+def clear_signs(bits, dtype):
+    """The operand's bit patterns with every sign bit cleared: |value| element by element."""
+    if dtype == abi.BF16:
+        return np.asarray(bits, dtype=np.uint16) & np.uint16(0x7FFF)
+    if dtype in (abi.FP8_143, abi.FP8_152):
+        return np.asarray(bits, dtype=np.uint8) & np.uint8(0x7F)
+    return np.abs(np.asarray(bits, dtype=np.float32))
+
+
+def conv_sum_abs(oracle, shapes, bits, dtype, cp, op, **tensor_kw):
+    """sum |a_k| |b_k| of every output of a convolution: the same operation run by the oracle on the operands'
+    absolute values (its own truncation errs by ~1e-6 relative, far inside its use as the scale of ACC_TOL)."""
+    T = abi.make_tensor
+    xs, ws, ys = shapes
+    xb, wb, yb = (clear_signs(b, dtype) for b in bits)
+    shp = {abi.OP_FWD: ys, abi.OP_DEDX: xs, abi.OP_DEDW: ws}[op]
+    out = np.zeros(int(np.prod(shp)), np.float32)
+    assert oracle.conv(T(out, abi.FP32, shp), T(xb, dtype, xs, **tensor_kw), T(wb, dtype, ws, **tensor_kw), T(yb, dtype, ys, **tensor_kw), cp, op) == 0
+    return out.astype(np.float64)
+
+
+def assert_acc(gpu, ref, sabs, name=""):
+    """The accumulator rule: |gpu - ref| <= ACC_TOL * sum|ab| for every element."""
+    err = acc_error(np.asarray(gpu).reshape(-1), np.asarray(ref).reshape(-1), np.asarray(sabs, dtype=np.float64).reshape(-1))
+    assert err <= ACC_TOL, "%s: accumulator error %.3g * sum|ab| exceeds %.0e" % (name, err, ACC_TOL)
+    return err
