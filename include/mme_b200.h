@@ -172,9 +172,9 @@ int mmeb200_set_accumulation(mmeb200_ctx* ctx, int mode);
  * picks tile shapes, K splits and store paths per problem; a knob forces one choice, value < 0 gives it back to the
  * planner. Names: "pair" (0/1: CTA-pair kernel), "block_n" (128/256: single-CTA tile width), "split_k" (n > 0),
  * "epi_groups" (1/2), "raster_gm" (m tiles per raster group), "tma_store" (0 = direct stores), "host_pipeline"
- * (0 = host-tensor GEMMs staged whole), "stream_k" (0 = no split of the last wave of tiles). The same knobs take their
+ * (0 = host-tensor GEMMs staged whole), "tile_n" (CTA-pair kernel: tile width, a multiple of 32 up to 256). The same knobs take their
  * defaults from environment variables read once in mmeb200_create (MME_B200_PAIR, MME_B200_BLOCK_N, MME_B200_SPLIT_K,
- * MME_B200_EPI_GROUPS, MME_B200_GM, MME_B200_NO_TMA_STORE, MME_B200_NO_HOST_PIPELINE, MME_B200_STREAM_K); no launch
+ * MME_B200_EPI_GROUPS, MME_B200_GM, MME_B200_NO_TMA_STORE, MME_B200_NO_HOST_PIPELINE, MME_B200_TILE_N); no launch
  * reads the environment. Results do not depend on the knobs beyond the accumulation tolerance (summation order). */
 int mmeb200_set_option(mmeb200_ctx* ctx, const char* name, int value);
 
@@ -315,30 +315,36 @@ int mmeb200_generate(mmeb200_ctx* ctx, mmeb200_tensor* out, const mmeb200_genera
 /* ---- dedw across the GPUs of one box, reduction fused with the exchange --------------------------
  * The reference sums partial weight gradients with doMemoryWrite's fp32 add
  * (mme_reference_impl.cpp:718-768; partial tensors: mme_verification/common/mme_test_manager.cpp:655-690).
- * Here every rank (one process per GPU) computes dW over its images and the kernel that reduces the
- * K-splits stores the result directly into slot [rank] of every rank's slot buffer over NVLink
- * (plain peer stores), signals every rank, waits -- bounded -- for all ranks' slots and adds them in
- * rank order: all ranks end with bit-identical sums, no host round trip, no separate collective.
- * Slot buffers and flags are allocated with mmeb200_peer_alloc, their handles exchanged by the caller
- * (any transport) and opened with mmeb200_peer_open. */
+ * Here every rank (one process per GPU) computes dW over its images, and the exchange is a reduce-scatter
+ * followed by an all-gather over peer memory, fused with the split-K reduction: the kernel that reduces the
+ * K-splits stores every element straight into the exchange buffer of the element's OWNER rank over NVLink
+ * (plain peer stores; nothing loads from a peer), each owner adds the `world` partials of its 1/world of dW
+ * in rank order and stores the sums to every rank: all ranks end with bit-identical sums, no host round
+ * trip, no separate collective, and 2 * (world-1)/world of dW leaves each rank. Every wait is bounded.
+ * Exchange buffers (mmeb200_peer_exchange_bytes) and flag blocks (256 bytes) are allocated with
+ * mmeb200_peer_alloc, their handles exchanged by the caller (any transport) and opened with mmeb200_peer_open. */
 #define MMEB200_MAX_PEERS 8
 #define MMEB200_PEER_HANDLE_BYTES 64
 typedef struct mmeb200_peer_group {
     int32_t rank, world;                 /* 1 <= world <= 8 */
-    void* slots[MMEB200_MAX_PEERS];      /* slots[j]: rank j's slot buffer (world * n fp32), addressable from this GPU */
-    uint32_t* flags[MMEB200_MAX_PEERS];  /* flags[j]: rank j's arrival counter (zero before the first exchange) */
+    void* slots[MMEB200_MAX_PEERS];      /* slots[j]: rank j's exchange buffer (mmeb200_peer_exchange_bytes), addressable from this GPU */
+    uint32_t* flags[MMEB200_MAX_PEERS];  /* flags[j]: rank j's flag block (256 bytes, zero before the first exchange) */
     uint32_t step;                       /* exchanges already done on this (slots, flags) set */
-    uint32_t deferred_output;            /* non-zero (device `out` only): the final wait-and-add runs on a side stream and
-                                            overlaps the next call's convolution; `out` is complete after the next
-                                            mmeb200_sync, and is ordered before the next exchange's output */
+    uint32_t deferred_output;            /* non-zero (device `out` only): the owner's sum and the final copy run on a side
+                                            stream and overlap the next call's convolution; `out` is complete after the
+                                            next mmeb200_sync, and is ordered before the next exchange's output */
 } mmeb200_peer_group;
+/* Bytes of one rank's exchange buffer for a result of n_floats fp32 values shared by `world` ranks: `world` partial
+ * slots of the rank's own segment plus the assembled result. */
+size_t mmeb200_peer_exchange_bytes(uint64_t n_floats, int world);
 /* cudaMalloc'd, zero-filled device memory plus the handle other processes open it with. */
 int mmeb200_peer_alloc(mmeb200_ctx* ctx, size_t bytes, void** dev_ptr, unsigned char handle[MMEB200_PEER_HANDLE_BYTES]);
 int mmeb200_peer_open(mmeb200_ctx* ctx, const unsigned char handle[MMEB200_PEER_HANDLE_BYTES], void** dev_ptr);
 int mmeb200_peer_close(mmeb200_ctx* ctx, void* dev_ptr);
 /* doConvolution(dedw) over this rank's x / y, summed over all ranks of `group` into `out` (fp32, dense,
- * the full dW). Consecutive calls must alternate between two (slots, flags) sets so that a fast rank
- * cannot overwrite slots a slow rank still reads; `step` counts the calls made on the set passed.
+ * the full dW; its element count must be a multiple of 4). Consecutive calls must alternate between two (slots, flags)
+ * sets so that a fast rank cannot overwrite slots a slow rank still reads; `step` counts the calls made on the set passed.
+ * Works in either accumulation mode (the bit-exact mode exchanges its exact partials the same way).
  * A rank that waits longer than about a second for its peers gets MMEB200_ERR_DEVICE_WAIT from the next
  * mmeb200_sync and stays usable. */
 int mmeb200_conv_dedw_allreduce(mmeb200_ctx* ctx, mmeb200_tensor* out, const mmeb200_tensor* x,

@@ -55,7 +55,7 @@ class CastParams(C.Structure):
 
 
 class PeerGroup(C.Structure):
-    """mmeb200_peer_group: slot buffers and arrival flags of the ranks taking part in a fused dedw exchange."""
+    """mmeb200_peer_group: exchange buffers and flag blocks of the ranks taking part in a fused dedw exchange."""
     _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("slots", C.c_void_p * 8), ("flags", C.c_void_p * 8),
                 ("step", C.c_uint32), ("deferred_output", C.c_uint32)]
 
@@ -171,6 +171,7 @@ SYMBOLS = {
     "mmeb200_compare": (C.c_int, [C.c_void_p, P(Tensor), P(Tensor), C.c_uint, C.c_uint, C.c_int, P(CompareResult)]),
     "mmeb200_set_accumulation": (C.c_int, [C.c_void_p, C.c_int]),
     "mmeb200_generate": (C.c_int, [C.c_void_p, P(Tensor), P(GenerateParams)]),
+    "mmeb200_peer_exchange_bytes": (C.c_size_t, [C.c_uint64, C.c_int]),
     "mmeb200_peer_alloc": (C.c_int, [C.c_void_p, C.c_size_t, P(C.c_void_p), C.c_char_p]),
     "mmeb200_peer_open": (C.c_int, [C.c_void_p, C.c_char_p, P(C.c_void_p)]),
     "mmeb200_peer_close": (C.c_int, [C.c_void_p, C.c_void_p]),

@@ -28,7 +28,7 @@ struct ArenaBlock {
 };
 
 // Tuning knobs of a context (-1 = let the planner decide). Their defaults come from the environment ONCE, when the
-// context is created (MME_B200_PAIR, _BLOCK_N, _SPLIT_K, _EPI_GROUPS, _GM, _NO_TMA_STORE, _NO_HOST_PIPELINE, _STREAM_K);
+// context is created (MME_B200_PAIR, _BLOCK_N, _SPLIT_K, _EPI_GROUPS, _GM, _NO_TMA_STORE, _NO_HOST_PIPELINE, _TILE_N);
 // mmeb200_set_option changes them per context afterwards. No launch reads the environment.
 struct Tuning {
     int pair = -1;            // 0 / 1: CTA-pair kernel off / on where it applies
@@ -38,7 +38,7 @@ struct Tuning {
     int raster_gm = -1;       // m tiles per raster group
     int tma_store = -1;       // 0: direct stores even where a TMA store applies
     int host_pipeline = -1;   // 0: host-tensor GEMMs are staged whole instead of pipelined
-    int stream_k = -1;        // 0: no tail split of the last wave
+    int tile_n = -1;          // CTA-pair kernel: forced tile width (a multiple of 32 in [32, 256])
 };
 static int env_int(const char* name, int dflt) {
     const char* e = getenv(name);
@@ -319,6 +319,65 @@ struct GemmJob {
     int force_split = 0;
 };
 
+static uint64_t peer_segment_floats(uint64_t n, int world) {
+    const uint64_t n4 = (n + 3) / 4;
+    return ((n4 + uint64_t(world) - 1) / uint64_t(world)) * 4;
+}
+
+// The cross-GPU sum of one fp32 result (dedw's partial dW): `splits` partial copies of n floats in `ws` are summed,
+// reduce-scattered to their owner ranks, summed there in rank order and all-gathered into `out` on every rank
+// (kernels.cuh: splitk_reduce_peer_scatter_kernel, peer_owner_sum_kernel, peer_result_copy_kernel).
+static int run_peer_exchange(mmeb200_ctx* c, const mmeb200_peer_group* peer, const float* ws, uint32_t splits, uint64_t n, float scale,
+                             float* out) {
+    if (n % 4) return c->fail(MMEB200_ERR_UNSUPPORTED, "the fused dedw exchange needs a result whose size is a multiple of 4");
+    const uint64_t seg = peer_segment_floats(n, peer->world);
+    PeerScatter ps;
+    memset(&ps, 0, sizeof ps);
+    PeerOwnerSum po;
+    memset(&po, 0, sizeof po);
+    for (int i = 0; i < peer->world; ++i) {
+        ps.bufs[i] = po.bufs[i] = static_cast<float*>(peer->slots[i]);
+        ps.flags[i] = po.flags[i] = peer->flags[i];
+    }
+    ps.block_counter = c->d_status + 8;
+    ps.rank = peer->rank; ps.world = peer->world; ps.splits = splits; ps.n = n; ps.seg = seg; ps.scale = scale;
+    po.block_counter = c->d_status + 9;
+    po.rank = peer->rank; po.world = peer->world; po.n = n; po.seg = seg;
+    po.target = uint32_t(peer->world) * (peer->step + 1);
+    po.status = c->d_status; po.limit_ns = 1000000000ull;
+    PeerResultCopy pc;
+    memset(&pc, 0, sizeof pc);
+    pc.my_buf = static_cast<const float*>(peer->slots[peer->rank]);
+    pc.my_flags = peer->flags[peer->rank];
+    pc.target = po.target; pc.world = peer->world; pc.n = n; pc.seg = seg; pc.out = out;
+    pc.status = c->d_status; pc.limit_ns = 1000000000ull;
+    const unsigned blocks = grid_for(n / 4, 256, c->sm_count);
+    const unsigned owner_blocks = grid_for(seg / 4, 256, c->sm_count);
+    const bool deferred = peer->deferred_output != 0;
+    if (deferred && !c->s_side) {
+        CUDA_OK(c, cudaStreamCreateWithFlags(&c->s_side, cudaStreamNonBlocking));
+        CUDA_OK(c, cudaEventCreateWithFlags(&c->ev_scatter, cudaEventDisableTiming));
+        CUDA_OK(c, cudaEventCreateWithFlags(&c->ev_gather, cudaEventDisableTiming));
+    }
+    // A rank may announce exchange i+1 only after it has read its buffers of exchange i: the partners' next-but-one stores
+    // reuse them, and they are held back only by this rank's arrivals.
+    if (c->gather_pending) CUDA_OK(c, cudaStreamWaitEvent(c->stream, c->ev_gather, 0));
+    splitk_reduce_peer_scatter_kernel<<<blocks, 256, 0, c->stream>>>(ws, ps);
+    cudaStream_t tail = c->stream;
+    if (deferred) {
+        CUDA_OK(c, cudaEventRecord(c->ev_scatter, c->stream));
+        CUDA_OK(c, cudaStreamWaitEvent(c->s_side, c->ev_scatter, 0));
+        tail = c->s_side;
+    }
+    peer_owner_sum_kernel<<<owner_blocks, 256, 0, tail>>>(po);
+    peer_result_copy_kernel<<<blocks, 256, 0, tail>>>(pc);
+    if (deferred) CUDA_OK(c, cudaEventRecord(c->ev_gather, c->s_side));
+    c->gather_pending = deferred;
+    c->launches += 3;
+    CUDA_OK(c, cudaGetLastError());
+    return 0;
+}
+
 static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     GemmParams p;
     memset(&p, 0, sizeof p);
@@ -349,15 +408,23 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     int block_n = wide ? 256 : 128;
     if (tune.block_n >= 0) { block_n = tune.block_n == 256 ? 256 : 128; use_pair = false; }
     uint64_t tiles, units;   // units = CTAs or CTA pairs the device runs at once
+    uint32_t tile_n = 256;
     if (use_pair) {
         p.m_tiles = (j.M + 255) / 256;
-        p.n_tiles = (j.N + 255) / 256;
-        block_n = 128;       // each CTA stages 128 of the pair's 256 columns of B
-        units = uint64_t(c->sm_count) / 2;
+        block_n = 128;       // each CTA stages (up to) 128 of the pair's columns of B
+        units = uint64_t(gemm_pair_capacity(launch_env(c), j.kind, 1));
+        if (units == 0) units = uint64_t(c->sm_count) / 2;
+        // Tile width: 256 unless the knob narrows it. Narrower tiles would fill a ragged last wave better (8192-wide outputs
+        // with 1024 rows: 4 x 37 tiles of 224 are exactly two waves of 74 pairs), but measured they lose: at 256 columns a
+        // k block's MMAs take as long as its 32 KB of operands take to arrive, so a narrower tile, which moves the same A
+        // for fewer columns, is bound by the operand feed (fp8 1024 x 8192 x 8192: 62 us at 256, 75 us at 224, 102 us at 128).
+        if (tune.tile_n > 0) tile_n = std::min(256, std::max(32, (tune.tile_n / 32) * 32));
+        p.n_tiles = (j.N + tile_n - 1) / tile_n;
     } else {
         p.n_tiles = (j.N + block_n - 1) / block_n;
         units = uint64_t(c->sm_count);
     }
+    p.tile_n = tile_n;
     p.raster_gm = 16;
     if (tune.raster_gm > 0) p.raster_gm = tune.raster_gm;
     tiles = uint64_t(p.m_tiles) * p.n_tiles * p.batches;
@@ -385,7 +452,7 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
         }
     }
     p.split_k = split;
-    p.idesc = use_pair ? make_instr_desc(j.a.hw_fmt, j.b.hw_fmt, j.a.mn_major, j.b.mn_major, 256, 256)
+    p.idesc = use_pair ? make_instr_desc(j.a.hw_fmt, j.b.hw_fmt, j.a.mn_major, j.b.mn_major, 256, tile_n)
                        : make_instr_desc(j.a.hw_fmt, j.b.hw_fmt, j.a.mn_major, j.b.mn_major, kBlockM, block_n);
     p.status = c->d_status;
     p.scale = o.scale;
@@ -412,6 +479,7 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
         // the raw fp32 partial(s) go to scratch; the peer kernels below finish the job
         if (p.batches != 1 || o.has_cast || (uint64_t(j.M) * j.N) % 4)
             return c->fail(MMEB200_ERR_UNSUPPORTED, "the fused dedw exchange needs a single fp32 result whose size is a multiple of 4");
+        if (o.dtype != DT_FP32) return c->fail(MMEB200_ERR_UNSUPPORTED, "the fused dedw exchange sums fp32 results");
         TRY(arena_alloc(c, &ws, size_t(split) * j.M * j.N * 4));
         p.out = ws;
         if (split == 1) { p.out_ld = j.N; p.scale = 1.0f; p.epi_mode = EPI_F32; p.has_cast = 0; p.out_dtype = DT_FP32; }
@@ -422,8 +490,15 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     if (j.a_im2col) p.tm_a = j.a_map;
     else if (!j.a.mn_major) TRY(encode_tiled(c, &p.tm_a, j.a, p.block_k, kBlockM));
     else TRY(encode_tiled(c, &p.tm_a, j.a, kRowBytes / elem, p.block_k));
-    if (!j.b.mn_major) TRY(encode_tiled(c, &p.tm_b, j.b, p.block_k, block_n));
-    else TRY(encode_tiled(c, &p.tm_b, j.b, kRowBytes / elem, p.block_k));
+    // B per CTA: block_n columns, or half a narrowed pair tile (whole 128-byte groups when N is the contiguous dimension)
+    const uint32_t b_cols = use_pair ? tile_n / 2 : uint32_t(block_n);
+    if (!j.b.mn_major) {
+        TRY(encode_tiled(c, &p.tm_b, j.b, p.block_k, b_cols));
+        p.b_cta_bytes = b_cols * kRowBytes;
+    } else {
+        TRY(encode_tiled(c, &p.tm_b, j.b, kRowBytes / elem, p.block_k));
+        p.b_cta_bytes = ((b_cols * elem + kRowBytes - 1) / kRowBytes) * p.block_k * kRowBytes;
+    }
     // coalesced TMA stores when the output's base and pitches allow a tensor map
     if (split == 1 && !peer && tune.tma_store != 0) {
         TmaOperand od;
@@ -446,45 +521,7 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
         rc = launch_status(c, launch_gemm_single(launch_env(c), j.kind, block_n, p, grid));
     }
     TRY(rc);
-    if (peer) {
-        const uint64_t n = uint64_t(j.M) * j.N;
-        PeerScatter ps;
-        memset(&ps, 0, sizeof ps);
-        for (int i = 0; i < peer->world; ++i) { ps.slots[i] = static_cast<float*>(peer->slots[i]); ps.flags[i] = peer->flags[i]; }
-        ps.block_counter = c->d_status + 8;
-        ps.rank = peer->rank; ps.world = peer->world; ps.splits = split; ps.n = n; ps.scale = o.scale;
-        const unsigned blocks = grid_for(n / 4, 256, c->sm_count);
-        const bool deferred = peer->deferred_output != 0;
-        if (deferred && !c->s_side) {
-            CUDA_OK(c, cudaStreamCreateWithFlags(&c->s_side, cudaStreamNonBlocking));
-            CUDA_OK(c, cudaEventCreateWithFlags(&c->ev_scatter, cudaEventDisableTiming));
-            CUDA_OK(c, cudaEventCreateWithFlags(&c->ev_gather, cudaEventDisableTiming));
-        }
-        // A rank may announce step i+1 only after it has read its slots of step i: the partners' next-but-one stores
-        // reuse them, and they are held back only by this rank's arrivals.
-        if (c->gather_pending) CUDA_OK(c, cudaStreamWaitEvent(c->stream, c->ev_gather, 0));
-        splitk_reduce_peer_scatter_kernel<<<blocks, 256, 0, c->stream>>>(static_cast<const float*>(ws), ps);
-        PeerGather pg;
-        memset(&pg, 0, sizeof pg);
-        pg.my_slots = static_cast<const float*>(peer->slots[peer->rank]);
-        pg.my_flag = peer->flags[peer->rank];
-        pg.target = uint32_t(peer->world) * (peer->step + 1);
-        pg.world = peer->world; pg.n = n; pg.out = static_cast<float*>(o.ptr); pg.status = c->d_status;
-        pg.limit_ns = 1000000000ull;
-        if (deferred) {
-            CUDA_OK(c, cudaEventRecord(c->ev_scatter, c->stream));
-            CUDA_OK(c, cudaStreamWaitEvent(c->s_side, c->ev_scatter, 0));
-            peer_gather_sum_kernel<<<blocks, 256, 0, c->s_side>>>(pg);
-            CUDA_OK(c, cudaEventRecord(c->ev_gather, c->s_side));
-            c->gather_pending = true;
-        } else {
-            peer_gather_sum_kernel<<<blocks, 256, 0, c->stream>>>(pg);
-            c->gather_pending = false;
-        }
-        c->launches += 2;
-        CUDA_OK(c, cudaGetLastError());
-        return 0;
-    }
+    if (peer) return run_peer_exchange(c, peer, static_cast<const float*>(ws), split, uint64_t(j.M) * j.N, o.scale, static_cast<float*>(o.ptr));
     if (split > 1) {
         ReduceOut r;
         memset(&r, 0, sizeof r);
@@ -837,7 +874,9 @@ static int bgemm_core(mmeb200_ctx* c, const mmeb200_tensor* out, const mmeb200_t
 static bool host_pipeline_applies(const mmeb200_ctx* c, const mmeb200_tensor* out, const mmeb200_tensor* x, const mmeb200_tensor* w, int op,
                                   const mmeb200_cast_params* cast, uint64_t M, uint64_t N, uint64_t K) {
     if (c->tune.host_pipeline == 0) return false;
-    if (out->mem_space != MMEB200_MEM_HOST || x->mem_space != MMEB200_MEM_HOST || w->mem_space != MMEB200_MEM_HOST) return false;
+    // x and the output stream through in row blocks; w is uploaded once, or is already resident (a multi-GPU driver that
+    // spread it over NVLink)
+    if (out->mem_space != MMEB200_MEM_HOST || x->mem_space != MMEB200_MEM_HOST) return false;
     if (op != MMEB200_OP_AB && op != MMEB200_OP_ABT) return false;  // rows of x must be rows of the product
     for (int d = 2; d < 5; ++d)
         if (out->sizes[d] != 1 || x->sizes[d] != 1 || w->sizes[d] != 1) return false;
@@ -854,7 +893,7 @@ static bool host_pipeline_applies(const mmeb200_ctx* c, const mmeb200_tensor* ou
     const uint64_t e = dtype_size(x->dtype);
     if ((K * e) % 16 || (reinterpret_cast<uintptr_t>(x->data) & 15)) return false;
     const uint64_t bytes = M * K * e + K * N * e + M * N * dtype_size(out->dtype);
-    return M >= 2048 && bytes >= (uint64_t(32) << 20);
+    return M >= 512 && bytes >= (uint64_t(32) << 20);
 }
 
 static int bgemm_host_pipelined(mmeb200_ctx* c, mmeb200_tensor* out, const mmeb200_tensor* x, const mmeb200_tensor* w, int op,
@@ -870,20 +909,21 @@ static int bgemm_host_pipelined(mmeb200_ctx* c, mmeb200_tensor* out, const mmeb2
     }
     const uint64_t e = dtype_size(x->dtype), eo = dtype_size(out->dtype);
     uint8_t *dA = nullptr, *dB = nullptr, *dO = nullptr;
+    const bool w_resident = w->mem_space == MMEB200_MEM_DEVICE;
     TRY(arena_alloc(c, reinterpret_cast<void**>(&dA), M * K * e));
-    TRY(arena_alloc(c, reinterpret_cast<void**>(&dB), K * N * e));
+    if (!w_resident) TRY(arena_alloc(c, reinterpret_cast<void**>(&dB), K * N * e));
     TRY(arena_alloc(c, reinterpret_cast<void**>(&dO), M * N * eo));
     // the arena may still be read by earlier work of this context's stream
     CUDA_OK(c, cudaEventRecord(c->ev_in[kMaxChunks], c->stream));
     CUDA_OK(c, cudaStreamWaitEvent(c->s_h2d, c->ev_in[kMaxChunks], 0));
     CUDA_OK(c, cudaStreamWaitEvent(c->s_d2h, c->ev_in[kMaxChunks], 0));
-    CUDA_OK(c, cudaMemcpyAsync(dB, w->data, K * N * e, cudaMemcpyHostToDevice, c->s_h2d));
+    if (!w_resident) CUDA_OK(c, cudaMemcpyAsync(dB, w->data, K * N * e, cudaMemcpyHostToDevice, c->s_h2d));
     // row blocks: multiples of the 128-row tile, about 8 of them
     uint64_t rows_per = ((M + 7) / 8 + 127) / 128 * 128;
     int nch = int((M + rows_per - 1) / rows_per);
     if (nch > kMaxChunks) { rows_per = ((M + kMaxChunks - 1) / kMaxChunks + 127) / 128 * 128; nch = int((M + rows_per - 1) / rows_per); }
     mmeb200_tensor tw = *w;
-    tw.data = dB; tw.mem_space = MMEB200_MEM_DEVICE;
+    if (!w_resident) { tw.data = dB; tw.mem_space = MMEB200_MEM_DEVICE; }
     for (int i = 0; i < nch; ++i) {
         const uint64_t r0 = uint64_t(i) * rows_per, rows = std::min<uint64_t>(rows_per, M - r0);
         CUDA_OK(c, cudaMemcpyAsync(dA + r0 * K * e, static_cast<const uint8_t*>(x->data) + r0 * K * e, rows * K * e, cudaMemcpyHostToDevice, c->s_h2d));
@@ -936,7 +976,7 @@ int mmeb200_create(mmeb200_ctx** out_ctx, int chip, int device, unsigned seed, u
     c->tune.raster_gm = env_int("MME_B200_GM", -1);
     c->tune.tma_store = getenv("MME_B200_NO_TMA_STORE") ? 0 : -1;
     c->tune.host_pipeline = getenv("MME_B200_NO_HOST_PIPELINE") ? 0 : -1;
-    c->tune.stream_k = env_int("MME_B200_STREAM_K", -1);
+    c->tune.tile_n = env_int("MME_B200_TILE_N", -1);
     if (cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) != cudaSuccess || cudaMalloc(&c->d_status, 64) != cudaSuccess ||
         cudaMallocHost(&c->h_status, 64) != cudaSuccess || cudaEventCreate(&c->ev0) != cudaSuccess || cudaEventCreate(&c->ev1) != cudaSuccess) {
         delete c;
@@ -998,7 +1038,7 @@ int mmeb200_set_option(mmeb200_ctx* c, const char* name, int value) {
     struct { const char* name; int Tuning::*field; } const table[] = {
         {"pair", &Tuning::pair}, {"block_n", &Tuning::block_n}, {"split_k", &Tuning::split_k}, {"epi_groups", &Tuning::epi_groups},
         {"raster_gm", &Tuning::raster_gm}, {"tma_store", &Tuning::tma_store}, {"host_pipeline", &Tuning::host_pipeline},
-        {"stream_k", &Tuning::stream_k}};
+        {"tile_n", &Tuning::tile_n}};
     for (const auto& t : table)
         if (strcmp(t.name, name) == 0) {
             c->tune.*(t.field) = value < 0 ? -1 : value;
@@ -1466,7 +1506,16 @@ int mmeb200_conv(mmeb200_ctx* c, mmeb200_tensor* out, const mmeb200_tensor* x, c
             }
         }
         const uint64_t ld = out->strides[1];
-        if (exact) {
+        if (exact && c->pending_peer) {
+            // bit-exact partial dW into scratch, then the same exchange as the tensor-core path
+            const mmeb200_peer_group* peer = c->pending_peer;
+            c->pending_peer = nullptr;
+            if (cast || !dense_out) return c->fail(MMEB200_ERR_UNSUPPORTED, "the fused dedw exchange needs a dense fp32 result");
+            void* part = nullptr;
+            TRY(arena_alloc(c, &part, M * N * 4));
+            TRY(run_exact_gemm(c, la, lb, M, N, part, N, one3, zero3));
+            TRY(run_peer_exchange(c, peer, static_cast<const float*>(part), 1, M * N, 1.0f, static_cast<float*>(so.t.data)));
+        } else if (exact) {
             if (!cast) TRY(run_exact_gemm(c, la, lb, M, N, so.t.data, ld, one3, zero3));
             else {
                 if (!dense_out) return c->fail(MMEB200_ERR_UNSUPPORTED, "a cast after bit-exact accumulation needs a dense output tensor");
@@ -1583,6 +1632,10 @@ int mmeb200_generate(mmeb200_ctx* c, mmeb200_tensor* out, const mmeb200_generate
 }
 
 // ------------------------------------------------------------------------------------------ dedw + exchange
+size_t mmeb200_peer_exchange_bytes(uint64_t n_floats, int world) {
+    if (world < 1 || world > MMEB200_MAX_PEERS) return 0;
+    return size_t(2) * size_t(world) * peer_segment_floats(n_floats, world) * sizeof(float);
+}
 int mmeb200_peer_alloc(mmeb200_ctx* c, size_t bytes, void** dev_ptr, unsigned char handle[MMEB200_PEER_HANDLE_BYTES]) {
     if (!c || !dev_ptr || !handle || bytes == 0) return MMEB200_ERR_INVALID_ARG;
     static_assert(sizeof(cudaIpcMemHandle_t) == MMEB200_PEER_HANDLE_BYTES, "handle size");
@@ -1622,7 +1675,10 @@ int mmeb200_conv_dedw_allreduce(mmeb200_ctx* c, mmeb200_tensor* out, const mmeb2
     if (out->mem_space != MMEB200_MEM_DEVICE) group.deferred_output = 0;   // a host output is copied back before the call returns
     c->pending_peer = &group;
     const int rc = mmeb200_conv(c, out, x, w, y, params, MMEB200_OP_DEDW, RM_NE, nullptr);
+    const bool consumed = c->pending_peer == nullptr;
     c->pending_peer = nullptr;
+    if (rc == 0 && !consumed)   // a path that produced only this rank's partial: the peers would wait for nothing
+        return c->fail(MMEB200_ERR_UNSUPPORTED, "this dedw took a path without the cross-GPU exchange (empty tensors?)");
     return rc;
 }
 

@@ -67,6 +67,8 @@ struct GemmParams {
     uint32_t num_k_blocks;  // over the whole K
     uint32_t m_tiles, n_tiles, batches, split_k;
     uint32_t raster_gm;     // m tiles per raster group: tiles of a group run together and share B panels in L2
+    uint32_t tile_n;        // CTA-pair kernel: columns of an output tile (a multiple of 32, at most 256); n_tiles counts these
+    uint32_t b_cta_bytes;   // CTA-pair kernel: bytes of B one CTA stages per k block (its tile_n / 2 columns)
     uint32_t bsz[3];
     uint32_t a_bcast[3], b_bcast[3];
     uint32_t a_mn_major, b_mn_major;
@@ -413,10 +415,11 @@ struct BFeed {
     uint32_t n_first, row, k_elem, k_wrap;
     int bb0, bb1, bb2;
 
-    __device__ __forceinline__ void setup(const GemmParams& p) {
+    // cols: columns this CTA stages (COLS, or fewer in the CTA-pair kernel when the planner narrows the tile)
+    __device__ __forceinline__ void setup(const GemmParams& p, uint32_t cols = COLS) {
         b_mn = p.b_mn_major != 0;
         tap_local = p.conv.b_tap_local != 0;
-        b_groups = b_mn ? (COLS * p.elem_bytes) / kRowBytes : 1;   // <= 8
+        b_groups = b_mn ? (cols * p.elem_bytes + kRowBytes - 1) / kRowBytes : 1;   // <= 8
         mn_group_elems = kRowBytes / p.elem_bytes;
         mn_group_bytes = p.block_k * kRowBytes;
         block_k = p.block_k;
@@ -452,11 +455,37 @@ struct BFeed {
     }
 };
 
-// Epilogue of one output tile, run by one epilogue warp for its 32 rows: reads BLOCK_N accumulator columns from
-// tensor memory (tmem_acc = the warp's lane window of the tile's accumulator), converts and stores them.
-// m0 is the first row of the CTA's 128-row block, n0 the first column.
-template <int BLOCK_N>
-__device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t m0, uint32_t n0, uint32_t batch, uint32_t split,
+// Stores 32 consecutive outputs of one row (v[0 .. 8 * elem) holds them packed) straight to global memory: 16-byte
+// stores when the 32 are all inside the matrix and the address allows, element stores on ragged edges.
+__device__ __forceinline__ void store_row32(const uint32_t (&v)[32], uint8_t* dst, uint32_t elem, uint32_t ncols) {
+    if (ncols == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+        if (elem == 4) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        } else if (elem == 2) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        }
+    } else {
+        // ragged edge or unaligned row: element-wise, statically indexed
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (uint32_t(j) < ncols) {
+                if (elem == 4) reinterpret_cast<uint32_t*>(dst)[j] = v[j];
+                else if (elem == 2) reinterpret_cast<uint16_t*>(dst)[j] = uint16_t(v[j / 2] >> (16 * (j & 1)));
+                else dst[j] = uint8_t(v[j / 4] >> (8 * (j & 3)));
+            }
+        }
+    }
+}
+
+// Epilogue of one output tile, run by one epilogue warp for its 32 rows: reads `tile_cols` accumulator columns (a
+// multiple of 32) from tensor memory (tmem_acc = the warp's lane window of the tile's accumulator), converts and stores
+// them. m0 is the first row of the CTA's 128-row block, n0 the first column.
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tile_cols, uint32_t m0, uint32_t n0, uint32_t batch, uint32_t split,
                                               uint32_t tmem_acc, uint8_t* stage_out, uint32_t& store_buf, uint32_t sub, uint32_t lane,
                                               uint32_t out_elem) {
     const uint32_t row = m0 + sub * 32 + lane;
@@ -468,9 +497,17 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t m0, 
         bi[2] = b;
     }
     const uint64_t flat_row = (uint64_t(batch) * p.M + row) * p.N;  // index base for the random stream
+    uint64_t base_off;
+    if (p.split_k > 1) {
+        base_off = (uint64_t(split) * p.batches + batch) * uint64_t(p.M) * p.N + uint64_t(row) * p.N;
+    } else {
+        base_off = bi[0] * p.out_bstride[0] + bi[1] * p.out_bstride[1] + bi[2] * p.out_bstride[2] + uint64_t(row) * p.out_ld;
+    }
+    uint32_t done_cols = 0;   // columns of the tile already stored
     if (p.tma_store) {
         // ---- stage 128-byte-wide column chunks in shared memory (128-byte swizzle) and let the
-        //      copy engine write them: full-line, coalesced stores, edges clipped by the tensor map
+        //      copy engine write them: full-line, coalesced stores, edges clipped by the tensor map.
+        //      Only whole chunks go this way: the columns after a narrowed tile's end belong to the next tile.
         const uint32_t cols_per_chunk = kRowBytes / out_elem;    // 32 fp32 / 64 bf16 / 128 fp8 columns
         const uint32_t lds_per_chunk = cols_per_chunk / 32;
         // each warp owns two 32-row x 128-byte buffers and issues its own stores: warps never
@@ -478,8 +515,9 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t m0, 
         uint8_t* my_bufs = stage_out + sub * (2 * 32 * kRowBytes);
         const uint32_t sw = (lane & 7);
 #pragma unroll 1
-        for (uint32_t ch = 0; ch < BLOCK_N / cols_per_chunk; ++ch) {
+        for (uint32_t ch = 0; ch < tile_cols / cols_per_chunk; ++ch) {
             const uint32_t col0 = n0 + ch * cols_per_chunk;
+            done_cols = (ch + 1) * cols_per_chunk;
             if (col0 >= p.N) break;  // uniform over the CTA
             uint8_t* buf = my_bufs + store_buf * (32 * kRowBytes);
             if (lane == 0) tma_store_wait_read<1>();   // the store issued two chunks ago has drained this buffer
@@ -513,54 +551,27 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t m0, 
             }
             store_buf ^= 1;
         }
-    } else {
-        uint64_t base_off;
-        if (p.split_k > 1) {
-            base_off = (uint64_t(split) * p.batches + batch) * uint64_t(p.M) * p.N + uint64_t(row) * p.N;
-        } else {
-            base_off = bi[0] * p.out_bstride[0] + bi[1] * p.out_bstride[1] + bi[2] * p.out_bstride[2] + uint64_t(row) * p.out_ld;
-        }
+    }
+    // ---- direct stores: everything when no tensor map applies (unaligned outputs, split-K partials), else the
+    //      columns left over after the last whole 128-byte chunk of a narrowed tile
 #pragma unroll 1
-        for (uint32_t ch = 0; ch < BLOCK_N / 32; ++ch) {
-            uint32_t v[32];
-            tmem_ld_32x32b_x32(tmem_acc + ch * 32, v);
-            tmem_ld_wait();
-            const uint32_t col0 = n0 + ch * 32;
-            if (row >= p.M || col0 >= p.N) continue;
-            const uint32_t ncols = min(32u, p.N - col0);
-            uint32_t elem = 4;
-            uint8_t* dst;
-            if (p.split_k > 1) {
-                dst = reinterpret_cast<uint8_t*>(reinterpret_cast<float*>(p.out) + base_off + col0);
-            } else {
-                elem = out_elem;
-                dst = reinterpret_cast<uint8_t*>(p.out) + (base_off + col0) * out_elem;
-                epilogue_convert(v, p, out_elem, flat_row + col0);
-            }
-            // v[0 .. 8*elem) now holds 32 packed outputs
-            if (ncols == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-                if (elem == 4) {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                } else if (elem == 2) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) reinterpret_cast<uint4*>(dst)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                }
-            } else {
-                // ragged edge or unaligned row: element-wise, statically indexed
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    if (uint32_t(j) < ncols) {
-                        if (elem == 4) reinterpret_cast<uint32_t*>(dst)[j] = v[j];
-                        else if (elem == 2) reinterpret_cast<uint16_t*>(dst)[j] = uint16_t(v[j / 2] >> (16 * (j & 1)));
-                        else dst[j] = uint8_t(v[j / 4] >> (8 * (j & 3)));
-                    }
-                }
-            }
+    for (uint32_t c0 = done_cols; c0 < tile_cols; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_acc + c0, v);
+        tmem_ld_wait();
+        const uint32_t col0 = n0 + c0;
+        if (row >= p.M || col0 >= p.N) continue;
+        const uint32_t ncols = min(32u, p.N - col0);
+        uint32_t elem = 4;
+        uint8_t* dst;
+        if (p.split_k > 1) {
+            dst = reinterpret_cast<uint8_t*>(reinterpret_cast<float*>(p.out) + base_off + col0);
+        } else {
+            elem = out_elem;
+            dst = reinterpret_cast<uint8_t*>(p.out) + (base_off + col0) * out_elem;
+            epilogue_convert(v, p, out_elem, flat_row + col0);
         }
+        store_row32(v, dst, elem, ncols);   // v[0 .. 8*elem) holds 32 packed outputs
     }
 }
 
@@ -719,7 +730,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
             }
             tc_fence_after_sync();
             const uint32_t tmem_acc = tmem_base + acc * BLOCK_N + ((sub * 32) << 16);
-            epilogue_tile<BLOCK_N>(p, tc.m0, n0, tc.batch, tc.split, tmem_acc, stage_out, store_buf, sub, lane, out_elem);
+            epilogue_tile(p, BLOCK_N, tc.m0, n0, tc.batch, tc.split, tmem_acc, stage_out, store_buf, sub, lane, out_elem);
             tc_fence_before_sync();
             mbar_arrive(&tmem_empty_bar[acc]);
             acc ^= 1;

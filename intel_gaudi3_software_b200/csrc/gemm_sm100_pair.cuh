@@ -21,7 +21,7 @@
 
 namespace mmeb200 {
 
-constexpr int kPairBlockN = 256;       // columns of the pair's tile; each CTA stages half of them
+constexpr int kPairBlockN = 256;       // most columns a pair's tile can have (p.tile_n of them are used); each CTA stages half
 
 // EPI_GROUPS = 1: four epilogue warps drain the CTA's 128 x 256 accumulator (six operand stages).
 // EPI_GROUPS = 2: eight epilogue warps, each group of four takes half of the columns (five stages; the
@@ -39,7 +39,10 @@ struct PairSmem {
     static constexpr int kThreads = 128 + 128 * EPI_GROUPS;
 };
 
-// p.m_tiles counts 256-row tiles here; p.n_tiles counts 256-column tiles.
+// p.m_tiles counts 256-row tiles here; p.n_tiles counts tiles of p.tile_n columns. The planner narrows tile_n (a
+// multiple of 32) when that fills the last wave of tiles better: one MMA then covers 256 x tile_n, CTA `rank` stages the
+// columns from rank * tile_n / 2 on (whole 128-byte groups of an MN-major B: up to 16 bytes' worth of columns more than it
+// needs), and the epilogue leaves the columns after tile_n to the next tile.
 template <int KIND, int EPI_GROUPS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<EPI_GROUPS>::kThreads, 1)
     gemm_tcgen05_pair_kernel(const __grid_constant__ GemmParams p) {
@@ -91,15 +94,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<EPI_GROUPS>
             bool ok = true;
             AFeed a_feed;
             BFeed<kPairBlockN / 2> b_feed;
-            if (is_a) a_feed.setup(p); else b_feed.setup(p);
-            const uint32_t my_bytes = is_a ? uint32_t(S::kABytes) : uint32_t(S::kBBytes);
+            if (is_a) a_feed.setup(p); else b_feed.setup(p, p.tile_n / 2);
+            const uint32_t my_bytes = is_a ? uint32_t(S::kABytes) : p.b_cta_bytes;
             const uint32_t dst_off = is_a ? 0u : uint32_t(S::kABytes);
             const uint32_t full0 = mapa_shared(smem_u32(&full_bar[0]), 0);   // the leader's full[0]
             for (uint32_t t = pair; t < total_tiles && ok; t += num_pairs) {
                 const TileCoord tc = decode_tile(p, t);
                 // first row (A) or column (B) this CTA stages
                 if (is_a) a_feed.begin_tile(p, tc.m0 * 2 + rank * kBlockM, tc.batch, tc.kb_begin);
-                else b_feed.begin_tile(p, tc.n0 * kPairBlockN + rank * (kPairBlockN / 2), tc.batch, tc.kb_begin);
+                else b_feed.begin_tile(p, tc.n0 * p.tile_n + rank * (p.tile_n / 2), tc.batch, tc.kb_begin);
                 for (uint32_t kb = tc.kb_begin; kb < tc.kb_end; ++kb) {
                     if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, kWaitLimitNs)) {
                         atomicCAS(p.status, 0u, WAIT_PRODUCER_EMPTY);
@@ -130,7 +133,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<EPI_GROUPS>
             const uint64_t a_step = (p.a_mn_major ? mn_k_step : uint32_t(kUmmaKBytes)) >> 4;
             const uint64_t b_step = (p.b_mn_major ? mn_k_step : uint32_t(kUmmaKBytes)) >> 4;
             constexpr uint64_t kStageUnits = S::kStageBytes >> 4;
-            const uint32_t idesc = p.idesc;   // M = 256, N = 256
+            const uint32_t idesc = p.idesc;   // M = 256, N = tile_n
             for (uint32_t t = pair; t < total_tiles && ok; t += num_pairs) {
                 const TileCoord tc = decode_tile(p, t);
                 if (!mbar_wait_bounded(&tmem_empty_bar[acc], acc_phase ^ 1, kWaitLimitNs)) {
@@ -184,8 +187,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<EPI_GROUPS>
             }
             tc_fence_after_sync();
             const uint32_t tmem_acc = tmem_base + acc * kPairBlockN + grp * kGroupCols + ((sub * 32) << 16);
-            epilogue_tile<kGroupCols>(p, tc.m0 * 2 + rank * kBlockM, tc.n0 * kPairBlockN + grp * kGroupCols, tc.batch, tc.split, tmem_acc,
-                                      stage_out, store_buf, sub, lane, out_elem);
+            const uint32_t group_cols = p.tile_n > grp * kGroupCols ? min(uint32_t(kGroupCols), p.tile_n - grp * kGroupCols) : 0u;
+            epilogue_tile(p, group_cols, tc.m0 * 2 + rank * kBlockM, tc.n0 * p.tile_n + grp * kGroupCols, tc.batch, tc.split, tmem_acc,
+                          stage_out, store_buf, sub, lane, out_elem);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(leader_tmem_empty + acc * 8);

@@ -421,25 +421,52 @@ __global__ void splitk_reduce_vec4_kernel(const float* __restrict__ ws, ReduceOu
 }
 
 // ---------------------------------------------------------------------------------------------
-// dedw across GPUs, fused with the split-K reduction: every rank sums its K-splits (ascending)
-// and stores the result straight into slot [rank] of EVERY rank's slot buffer over NVLink (plain
-// peer stores only), then bumps an arrival counter on every rank. A second kernel
-// waits (bounded) until all ranks have arrived and adds the slots in rank order, so all ranks hold
-// bit-identical sums. This is the multi-GPU form of summing dedw partials with doMemoryWrite's
-// fp32 add (mme/mme_reference/mme_reference_impl.cpp:718-768).
+// dedw across GPUs, fused with the split-K reduction, as a reduce-scatter followed by an all-gather
+// over peer memory (plain peer stores over NVLink only; nothing ever LOADS from a peer):
+//   1. splitk_reduce_peer_scatter_kernel: every rank sums its K-splits (ascending) and stores each
+//      element into the slot buffer of the element's OWNER (rank j owns elements [j*seg, (j+1)*seg)),
+//      at slot [sender]; then it bumps arrival counter A on every rank.
+//   2. peer_owner_sum_kernel: the owner waits (bounded) until all `world` senders have arrived, adds
+//      the `world` slots of its segment in rank order -- so every rank later holds the same bits --
+//      and stores the sums into the result buffer of every rank; then it bumps arrival counter B.
+//   3. peer_result_copy_kernel: waits (bounded) until all owners have delivered and copies the
+//      assembled result to the caller's tensor.
+// Bytes leaving a rank per exchange: 2 * (world-1)/world * n * 4 (an all-to-all of whole partials
+// would send (world-1) * n * 4). This is the multi-GPU form of summing dedw partials with
+// doMemoryWrite's fp32 add (mme/mme_reference/mme_reference_impl.cpp:718-768; partial-sum model of
+// mme/mme_verification/common/mme_test_manager.cpp:655-690).
+// Buffer of rank j (PeerExchangeLayout): [world x seg floats of slots][world x seg floats of result];
+// flag block of rank j: counter A at word 0, counter B at word 32.
 // ---------------------------------------------------------------------------------------------
 constexpr int kMaxPeers = 8;
+constexpr uint32_t kPeerFlagBWord = 32;
 struct PeerScatter {
-    float* slots[kMaxPeers];      // slots[j] = base of rank j's slot buffer: world x n floats
-    uint32_t* flags[kMaxPeers];   // flags[j] = arrival counter living on rank j
+    float* bufs[kMaxPeers];       // bufs[j] = base of rank j's exchange buffer
+    uint32_t* flags[kMaxPeers];   // flags[j] = flag block living on rank j
     uint32_t* block_counter;      // local: counts finished blocks of this launch (reset by the last one)
     uint32_t rank, world, splits;
-    uint64_t n;                   // floats per slot (M * N)
+    uint64_t n;                   // floats of the whole result (M * N), a multiple of 4
+    uint64_t seg;                 // floats per owner segment, a multiple of 4; world * seg >= n
     float scale;
 };
 
+// The last block of a launch to finish tells every rank, through the counter at flag word `word`, that this rank's
+// stores are complete: every thread's peer stores are fenced before its block's arrival.
+__device__ __forceinline__ void peer_publish(uint32_t* block_counter, uint32_t* const* flags, uint32_t world, uint32_t word) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t done = atomicAdd(block_counter, 1u) + 1;
+        if (done == gridDim.x) {
+            *block_counter = 0;
+            __threadfence_system();
+            for (uint32_t j = 0; j < world; ++j) atomicAdd_system(flags[j] + word, 1u);
+        }
+    }
+}
+
 __global__ void splitk_reduce_peer_scatter_kernel(const float* __restrict__ ws, PeerScatter p) {
-    const uint64_t n4 = p.n / 4;  // the host guarantees n % 4 == 0
+    const uint64_t n4 = p.n / 4, seg4 = p.seg / 4;
     const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
     for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -448,36 +475,11 @@ __global__ void splitk_reduce_peer_scatter_kernel(const float* __restrict__ ws, 
             s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
         }
         s.x *= p.scale; s.y *= p.scale; s.z *= p.scale; s.w *= p.scale;
-        // start with the next rank so that the eight senders do not all hit the same receiver at once
-        for (uint32_t d = 0; d < p.world; ++d) {
-            const uint32_t j = (p.rank + 1 + d) % p.world;
-            reinterpret_cast<float4*>(p.slots[j] + uint64_t(p.rank) * p.n)[i] = s;
-        }
+        const uint64_t owner = i / seg4, local = i - owner * seg4;
+        reinterpret_cast<float4*>(p.bufs[owner] + uint64_t(p.rank) * p.seg)[local] = s;
     }
-    // publish: every thread's peer stores are ordered before the block's arrival; the last block of
-    // the launch then tells every rank that this rank's slot is complete
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const uint32_t done = atomicAdd(p.block_counter, 1u) + 1;
-        if (done == gridDim.x) {
-            *p.block_counter = 0;
-            __threadfence_system();
-            for (uint32_t j = 0; j < p.world; ++j) atomicAdd_system(p.flags[j], 1u);
-        }
-    }
+    peer_publish(p.block_counter, p.flags, p.world, 0);
 }
-
-struct PeerGather {
-    const float* my_slots;        // this rank's slot buffer: world x n floats
-    const uint32_t* my_flag;      // this rank's arrival counter
-    uint32_t target;              // value the counter reaches when every rank has delivered this exchange
-    uint32_t world;
-    uint64_t n;
-    float* out;
-    uint32_t* status;
-    uint64_t limit_ns;
-};
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     uint32_t v;
@@ -485,37 +487,80 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     return v;
 }
 
-__global__ void peer_gather_sum_kernel(PeerGather p) {
+// Thread 0 of the block waits until *flag reaches `target` (wrap-safe compare), for at most limit_ns; on expiry it records
+// `code` in the status word. Returns to every thread of the block whether the wait succeeded.
+__device__ __forceinline__ bool peer_wait(const uint32_t* flag, uint32_t target, uint64_t limit_ns, uint32_t* status, uint32_t code) {
     __shared__ int ok;
     if (threadIdx.x == 0) {
-        // wrap-safe compare; the wait is bounded: on expiry the kernel reports and leaves
         uint64_t t0;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
         int good = 1;
         uint32_t spins = 0;
-        while (int32_t(ld_acquire_sys(p.my_flag) - p.target) < 0) {
+        while (int32_t(ld_acquire_sys(flag) - target) < 0) {
             if ((++spins & 0xff) == 0) {
                 uint64_t t;
                 asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-                if (t - t0 > p.limit_ns) { good = 0; break; }
+                if (t - t0 > limit_ns) { good = 0; break; }
             }
         }
-        if (!good) atomicCAS(p.status, 0u, 16u);
+        if (!good) atomicCAS(status, 0u, code);
         ok = good;
     }
     __syncthreads();
-    if (!ok) return;
-    const uint64_t n4 = p.n / 4;
+    return ok != 0;
+}
+
+struct PeerOwnerSum {
+    float* bufs[kMaxPeers];
+    uint32_t* flags[kMaxPeers];
+    uint32_t* block_counter;
+    uint32_t rank, world;
+    uint32_t target;              // value counter A reaches when every rank has sent this exchange's partials
+    uint64_t n, seg;
+    uint32_t* status;
+    uint64_t limit_ns;
+};
+
+__global__ void peer_owner_sum_kernel(PeerOwnerSum p) {
+    if (!peer_wait(p.flags[p.rank], p.target, p.limit_ns, p.status, 16u)) return;
+    const uint64_t begin = uint64_t(p.rank) * p.seg;
+    const uint64_t mine4 = (begin >= p.n ? 0 : (p.n - begin < p.seg ? p.n - begin : p.seg)) / 4;
+    const float* slots = p.bufs[p.rank];
     const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
-    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < mine4; i += stride) {
         float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
         for (uint32_t r = 0; r < p.world; ++r) {
-            // slots were written by other GPUs: read them past L1
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(p.my_slots + uint64_t(r) * p.n) + i);
+            // the slots were written by other GPUs: read them past L1
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(slots + uint64_t(r) * p.seg) + i);
             s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
         }
-        reinterpret_cast<float4*>(p.out)[i] = s;
+        // start with the next rank so that the owners do not all hit the same receiver at once
+        for (uint32_t d = 0; d < p.world; ++d) {
+            const uint32_t j = (p.rank + 1 + d) % p.world;
+            reinterpret_cast<float4*>(p.bufs[j] + uint64_t(p.world) * p.seg + begin)[i] = s;
+        }
     }
+    peer_publish(p.block_counter, p.flags, p.world, kPeerFlagBWord);
+}
+
+struct PeerResultCopy {
+    const float* my_buf;          // this rank's exchange buffer
+    const uint32_t* my_flags;     // this rank's flag block
+    uint32_t target;              // value counter B reaches when every owner has delivered this exchange's sums
+    uint32_t world;
+    uint64_t n, seg;
+    float* out;
+    uint32_t* status;
+    uint64_t limit_ns;
+};
+
+__global__ void peer_result_copy_kernel(PeerResultCopy p) {
+    if (!peer_wait(p.my_flags + kPeerFlagBWord, p.target, p.limit_ns, p.status, 17u)) return;
+    const float4* src = reinterpret_cast<const float4*>(p.my_buf + uint64_t(p.world) * p.seg);
+    const uint64_t n4 = p.n / 4;
+    const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride)
+        reinterpret_cast<float4*>(p.out)[i] = __ldcg(src + i);
 }
 
 // ---------------------------------------------------------------------------------------------

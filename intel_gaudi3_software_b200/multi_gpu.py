@@ -42,8 +42,38 @@ class ShardedCalculator:
     on a torch tensor that aliases the partial dW.
     """
 
-    def __init__(self, calc, dist=None, rank=0, world=1):
+    def __init__(self, calc, dist=None, rank=0, world=1, device=None):
         self.calc, self.dist, self.rank, self.world = calc, dist, rank, world
+        self.device = getattr(calc, "device", 0) if device is None else device
+        self._shared_b = None
+
+    def host_gemm_shared_b(self, out, x, w, op, cast=None):
+        """Host-tensor GEMM of this rank's rows (`x`, `out`: this rank's shards in pinned host memory) by a `w` that is
+        the same on every rank. Instead of `world` uploads of the whole of w through the one host, each rank uploads
+        1/world of it over PCIe and the ranks all-gather the pieces over NVLink (NCCL); the library then streams the rows
+        of x and of the output through the GPU around the resident w."""
+        import torch
+        calc, world, rank = self.calc, self.world, self.rank
+        nbytes = int(np.prod(list(w.sizes))) * abi.ELEM_SIZE[w.dtype]
+        piece = ((nbytes + world - 1) // world + 15) // 16 * 16
+        if self._shared_b is None or self._shared_b.numel() != piece * world:
+            self._shared_b = torch.empty(piece * world, dtype=torch.uint8, device=torch.device("cuda", self.device))
+        buf = self._shared_b
+        stream = torch.cuda.current_stream(buf.device)
+        calc.set_stream(stream.cuda_stream)
+        begin = rank * piece
+        mine = max(0, min(piece, nbytes - begin))
+        if mine:
+            calc._check(calc.lib.mmeb200_memcpy_h2d(calc.ctx, buf.data_ptr() + begin, (w.data or 0) + begin, mine))
+        if world > 1:
+            self.dist.all_gather_into_tensor(buf, buf[begin:begin + piece])
+        wd = abi.Tensor()
+        abi.C.memmove(abi.C.byref(wd), abi.C.byref(w), abi.C.sizeof(abi.Tensor))
+        wd.data, wd.mem_space = buf.data_ptr(), abi.MEM_DEVICE
+        try:
+            calc.do_batch_gemm(out, x, wd, op, cast)
+        finally:
+            calc.set_stream(None)
 
     def batch_gemm_rows(self, out, x, w, op, cast=None):
         """Each rank computes its block of output rows (op ab / abt: rows of x are rows of the output)."""
@@ -80,23 +110,23 @@ class ShardedCalculator:
 
 
 class PeerExchange:
-    """Slot buffers and flags for the fused dedw exchange (mmeb200_conv_dedw_allreduce), double-buffered.
+    """Exchange buffers and flag blocks for the fused dedw exchange (mmeb200_conv_dedw_allreduce), double-buffered.
 
-    Every rank allocates two slot buffers (world x n fp32) and two flags, publishes their handles with
+    Every rank allocates two exchange buffers (mmeb200_peer_exchange_bytes) and two flag blocks, publishes their handles with
     `all_gather_object` (any torch.distributed backend; world == 1 needs none) and opens the peers'.
     `dedw_allreduce` alternates between the two sets, which is what lets ranks drift apart by one step.
     """
 
     def __init__(self, calc, n_floats, dist=None, rank=0, world=1, deferred_output=False):
-        """deferred_output: with a device-resident `out`, the final wait-and-add of an exchange overlaps the next call's
-        convolution; `out` is then complete after the calculator's next sync()."""
+        """deferred_output: with a device-resident `out`, the owner's sum and the final copy of an exchange overlap the next
+        call's convolution; `out` is then complete after the calculator's next sync()."""
         assert 1 <= world <= 8
         self.calc, self.rank, self.world, self.n = calc, rank, world, n_floats
         self.deferred_output = deferred_output
         self.calls = 0
         mine = []
         for _ in range(2):
-            slots, hs = calc.peer_alloc(world * n_floats * 4)
+            slots, hs = calc.peer_alloc(calc.lib.mmeb200_peer_exchange_bytes(n_floats, world))
             flag, hf = calc.peer_alloc(256)
             mine.append((slots, hs, flag, hf))
         handles = [[(m[1], m[3]) for m in mine]]

@@ -30,8 +30,12 @@ def main():
     cp = abi.make_conv_params(2, (1, 1), (1, 1), (1, 1))
     n = int(np.prod(ws))
     # the whole batch on one GPU: what the sum over ranks must equal (up to the order of summation)
-    full = np.zeros(n, np.float32)
+    full, sabs = np.zeros(n, np.float32), np.zeros(n, np.float32)
     calc.do_convolution(T(full, abi.FP32, ws), T(xb, abi.BF16, xs), T(wb, abi.BF16, ws), T(yb, abi.BF16, ys), cp, abi.OP_DEDW)
+    # sum|a_k b_k| per element: the same dedw on the operands' absolute values (the scale of the accumulator tolerance)
+    calc.do_convolution(T(sabs, abi.FP32, ws), T(util.clear_signs(xb, abi.BF16), abi.BF16, xs), T(wb, abi.BF16, ws),
+                        T(util.clear_signs(yb, abi.BF16), abi.BF16, ys), cp, abi.OP_DEDW)
+    tol = util.ACC_TOL * sabs.astype(np.float64)
     b0, b1 = shard_range(B, world, rank)
     per_x, per_y = int(np.prod(xs[:3])), int(np.prod(ys[:3]))
     xs_r, ys_r = xs[:3] + [b1 - b0], ys[:3] + [b1 - b0]
@@ -41,7 +45,7 @@ def main():
     for it in range(6):
         out = np.zeros(n, np.float32)
         ex.dedw_allreduce(T(out, abi.FP32, ws), T(xr, abi.BF16, xs_r), T(wb, abi.BF16, ws), T(yr, abi.BF16, ys_r), cp)
-        ok &= bool(np.abs(out - full).max() <= 2e-5 * np.abs(full).max())
+        ok &= bool((np.abs(out.astype(np.float64) - full) <= tol).all())
         # all ranks must hold bit-identical sums
         t = torch.from_numpy(out.view(np.int32).copy()).cuda()
         lo, hi = t.clone(), t.clone()
@@ -59,7 +63,7 @@ def main():
                            T(dw.ptr, abi.BF16, ws, mem_space=dev), T(dy.ptr, abi.BF16, ys_r, mem_space=dev), cp)
     calc.sync(10_000_000_000)
     out = dout.download(np.float32)
-    ok &= bool(np.abs(out - full).max() <= 2e-5 * np.abs(full).max())
+    ok &= bool((np.abs(out.astype(np.float64) - full) <= tol).all())
     t = torch.from_numpy(out.view(np.int32).copy()).cuda()
     lo, hi = t.clone(), t.clone()
     dist.all_reduce(lo, op=dist.ReduceOp.MIN)
@@ -67,6 +71,21 @@ def main():
     ok &= bool((lo == hi).all().item())
     dist.barrier()
     ex2.close()
+    # the bit-exact accumulation mode: exact partials per rank, same exchange, bit-identical sums on all ranks
+    exact = pkg.Calculator(device=local, accumulation=abi.ACC_CHIP_EXACT)
+    ex3 = PeerExchange(exact, n, dist, rank, world)
+    for it in range(2):
+        out = np.zeros(n, np.float32)
+        ex3.dedw_allreduce(T(out, abi.FP32, ws), T(xr, abi.BF16, xs_r), T(wb, abi.BF16, ws), T(yr, abi.BF16, ys_r), cp)
+        ok &= bool((np.abs(out.astype(np.float64) - full) <= tol).all())
+        t = torch.from_numpy(out.view(np.int32).copy()).cuda()
+        lo, hi = t.clone(), t.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        ok &= bool((lo == hi).all().item())
+    dist.barrier()
+    ex3.close()
+    exact.close()
     calc.close()
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)

@@ -58,7 +58,9 @@ KERNEL_VARIANTS = {
     "pair, four epilogue warps": {"pair": 1, "epi_groups": 1},
     "pair, eight epilogue warps": {"pair": 1, "epi_groups": 2},
     "pair, split-K": {"pair": 1, "split_k": 3},
-    "pair, no split of the last wave": {"pair": 1, "stream_k": 0},
+    "pair, 224-wide tiles": {"pair": 1, "tile_n": 224},
+    "pair, 160-wide tiles, eight epilogue warps": {"pair": 1, "tile_n": 160, "epi_groups": 2},
+    "pair, 96-wide tiles": {"pair": 1, "tile_n": 96},
     "single CTA, 256 wide": {"pair": 0},
     "single CTA, 128 wide": {"block_n": 128},
     "single CTA, no TMA stores": {"pair": 0, "tma_store": 0},

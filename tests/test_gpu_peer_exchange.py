@@ -1,7 +1,8 @@
-"""The fused dedw exchange (split-K reduction + peer stores + rank-ordered gather).
+"""The fused dedw exchange (split-K reduction + reduce-scatter to the owner ranks + rank-ordered sum + all-gather, all over
+plain peer stores).
 
-One GPU: a group of world 1 runs the same kernels (scatter into its own slot, flag, bounded wait, gather)
-and must reproduce plain dedw bit for bit. Two or more GPUs: one process per GPU over real peer memory
+One GPU: a group of world 1 runs the same kernels (scatter into its own slot, flags, bounded waits, owner sum, copy)
+and must reproduce plain dedw bit for bit, in the tensor-core mode and in the bit-exact accumulation mode. Two or more GPUs: one process per GPU over real peer memory
 (skipped where fewer GPUs are visible). A wait that cannot be satisfied (a flag nobody sets) must end by
 itself with MMEB200_ERR_DEVICE_WAIT and leave the context usable -- no GPU fault is involved."""
 import os
@@ -44,6 +45,24 @@ def test_world_of_one_matches_plain_dedw(calc):
         ex.dedw_allreduce(T(fused, abi.FP32, CASE["ws"]), x, w, y, cp)
         assert (fused.view(np.uint32) == plain.view(np.uint32)).all(), it
     ex.close()
+
+
+def test_world_of_one_in_the_exact_accumulation_mode():
+    """The bit-exact mode takes the general lowering (im2col + exact GEMM); its partial dW must go through the same exchange."""
+    c = pkg.Calculator(device=0, accumulation=abi.ACC_CHIP_EXACT)
+    xb, wb, yb = inputs(3)
+    cp = abi.make_conv_params(2, (1, 1), (1, 1), (1, 1))
+    x, w, y = T(xb, abi.BF16, CASE["xs"]), T(wb, abi.BF16, CASE["ws"]), T(yb, abi.BF16, CASE["ys"])
+    n = int(np.prod(CASE["ws"]))
+    plain = np.zeros(n, np.float32)
+    c.do_convolution(T(plain, abi.FP32, CASE["ws"]), x, w, y, cp, abi.OP_DEDW)
+    ex = PeerExchange(c, n)
+    for it in range(3):
+        fused = np.full(n, 9.0, np.float32)
+        ex.dedw_allreduce(T(fused, abi.FP32, CASE["ws"]), x, w, y, cp)
+        assert (fused.view(np.uint32) == plain.view(np.uint32)).all(), it
+    ex.close()
+    c.close()
 
 
 def test_world_of_one_deferred_output_on_device_tensors(calc):
