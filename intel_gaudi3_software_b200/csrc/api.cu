@@ -1723,7 +1723,7 @@ int mmeb200_memory_write(mmeb200_ctx* c, mmeb200_tensor* mem, const mmeb200_tens
         TRY(stage_in(c, mme_out, &so, true));
         TRY(stage_in(c, mem, &sm, false));
         CUDA_OK(c, cudaMemcpyAsync(sm.t.data, so.t.data, n * dtype_size(mem->dtype), cudaMemcpyDeviceToDevice, c->stream));
-    } else if (red_op >= MMEB200_RED_ADD && red_op <= MMEB200_RED_MAX_0 && (mem->dtype == DT_FP32 || mem->dtype == DT_BF16)) {
+    } else if (red_op >= MMEB200_RED_ADD && red_op <= MMEB200_RED_MAX_0 && (mem->dtype == DT_FP32 || mem->dtype == DT_BF16 || mem->dtype == DT_FP8_152)) {
         if (red_rm < 0 || red_rm > 3) return c->fail(MMEB200_ERR_INVALID_ARG, "reduction rounding mode %d is not valid", red_rm);
         TRY(stage_in(c, mme_out, &so, true));
         TRY(stage_in(c, mem, &sm, true));
@@ -1731,6 +1731,14 @@ int mmeb200_memory_write(mmeb200_ctx* c, mmeb200_tensor* mem, const mmeb200_tens
             memory_write_f32_kernel<<<grid_for((n + 7) / 8, 256, c->sm_count), 256, 0, c->stream>>>(static_cast<uint32_t*>(sm.t.data),
                                                                                          static_cast<const uint32_t*>(so.t.data), n,
                                                                                          red_op, red_rm, clip_fp);
+            c->launches++;
+        } else if (n && mem->dtype == DT_FP8_152) {
+            // the reference's fp8 RMW type is 1-5-2 with the hardware bias and the full Inf/NaN convention (fs_fma.cpp:2410-2435)
+            if (mem->fp_bias != 15 || mme_out->fp_bias != 15 || mem->inf_nan_mode != 0)
+                return c->fail(MMEB200_ERR_UNSUPPORTED, "fp8_152 reductions are defined for exponent bias 15 and the full Inf/NaN convention");
+            memory_write_fp8_152_kernel<<<grid_for((n + 15) / 16, 256, c->sm_count), 256, 0, c->stream>>>(static_cast<uint8_t*>(sm.t.data),
+                                                                                               static_cast<const uint8_t*>(so.t.data), n,
+                                                                                               red_op, red_rm, clip_fp);
             c->launches++;
         } else if (n) {
             memory_write_bf16_kernel<<<grid_for((n + 7) / 8, 256, c->sm_count), 256, 0, c->stream>>>(static_cast<uint16_t*>(sm.t.data),

@@ -87,6 +87,10 @@ void hc_bf16_rmw(uint16_t* mem, const uint16_t* in, size_t n, int op, int rm, in
 {
     for (size_t i = 0; i < n; i++) mem[i] = uint16_t(bf16_rmw(mem[i], in[i], op, rm, clip != 0));
 }
+void hc_fp8_152_rmw(uint8_t* mem, const uint8_t* in, size_t n, int op, int rm, int clip)
+{
+    for (size_t i = 0; i < n; i++) mem[i] = uint8_t(fp8_152_rmw(mem[i], in[i], op, rm, clip != 0));
+}
 // dot product of n decoded fp32 bit patterns in the reference's block order (blocks of eight, zero-padded tail)
 uint32_t hc_g3_dot(const uint32_t* a, const uint32_t* b, size_t n)
 {

@@ -156,9 +156,25 @@ def test_memory_write_bf16(calc, port):
                 assert port.memory_write(T(m1, abi.BF16, [n]), T(b.copy(), abi.BF16, [n]), op, rm, clip) == 0
                 calc.do_memory_write(T(m2, abi.BF16, [n]), T(b.copy(), abi.BF16, [n]), op, rm, clip)
                 assert (m1 == m2).all(), (op, rm, clip, int((m1 != m2).sum()))
-    with pytest.raises(Exception, match="not implemented"):
+    with pytest.raises(Exception, match="not implemented"):   # the reference rejects fp8_143 reductions too
         x = np.zeros(16, np.uint8)
-        calc.do_memory_write(T(x, abi.FP8_152, [16]), T(x.copy(), abi.FP8_152, [16]), abi.RED_ADD, 0)
+        calc.do_memory_write(T(x, abi.FP8_143, [16], fp_bias=7), T(x.copy(), abi.FP8_143, [16], fp_bias=7), abi.RED_ADD, 0)
+
+
+def test_memory_write_fp8_152_every_operand_pair(calc, port):
+    """All 256 x 256 pairs of codes (twice over, plus a ragged tail, so the vector path and the scalar tail both run), every
+    reduction, direction and clip flag, bit for bit against the oracle."""
+    a = np.concatenate([np.repeat(np.arange(256, dtype=np.uint8), 256)] * 2 + [np.arange(7, dtype=np.uint8)])
+    b = np.concatenate([np.tile(np.arange(256, dtype=np.uint8), 256)] * 2 + [np.arange(7, dtype=np.uint8)[::-1]])
+    n = a.size
+    kw = dict(fp_bias=15, inf_nan_mode=abi.INFNAN_FULL)
+    for op in (abi.RED_ADD, abi.RED_SUB, abi.RED_MIN, abi.RED_MAX, abi.RED_MAX_0):
+        for rm in (0, 1, 2, 3):
+            for clip in (0, 1):
+                m1, m2 = a.copy(), a.copy()
+                assert port.memory_write(T(m1, abi.FP8_152, [n], **kw), T(b.copy(), abi.FP8_152, [n], **kw), op, rm, clip) == 0
+                calc.do_memory_write(T(m2, abi.FP8_152, [n], **kw), T(b.copy(), abi.FP8_152, [n], **kw), op, rm, clip)
+                assert (m1 == m2).all(), (op, rm, clip, int((m1 != m2).sum()))
 
 
 def test_dma_transpose_and_copy(calc):

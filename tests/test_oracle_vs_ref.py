@@ -116,6 +116,22 @@ def test_memory_write_reductions(port, ref):
                 assert same(m1, m2), (op, rm, clip)
 
 
+def test_memory_write_fp8_152_reductions_on_every_operand_pair(port, ref):
+    a = np.repeat(np.arange(256, dtype=np.uint8), 256)
+    b = np.tile(np.arange(256, dtype=np.uint8), 256)
+    n = a.size
+    for op in (abi.RED_ADD, abi.RED_SUB, abi.RED_MIN, abi.RED_MAX, abi.RED_MAX_0):
+        for rm in (0, 1, 2, 3):
+            for clip in (False, True):
+                if op in (abi.RED_MIN, abi.RED_MAX) and (rm or clip):
+                    continue
+                m1, m2 = a.copy(), a.copy()
+                assert port.memory_write(T(m1, abi.FP8_152, [n], fp_bias=15), T(b.copy(), abi.FP8_152, [n], fp_bias=15), op, rm, clip) == 0
+                assert ref.memory_write(T(m2, abi.FP8_152, [n], fp_bias=15), T(b.copy(), abi.FP8_152, [n], fp_bias=15), op, rm, clip) == 0
+                bad = np.nonzero(m1 != m2)[0]
+                assert bad.size == 0, (op, rm, clip, bad.size, [(hex(a[i]), hex(b[i]), hex(m1[i]), hex(m2[i])) for i in bad[:8]])
+
+
 def test_memory_write_bf16_reductions(port, ref):
     from test_numerics_host import bf16_operand_pairs
     a, b = bf16_operand_pairs(np.random.default_rng(29), 120000)
