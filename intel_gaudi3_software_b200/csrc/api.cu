@@ -317,6 +317,8 @@ struct GemmJob {
     uint32_t kind = KIND_F16;
     uint32_t bsz[3] = {1, 1, 1};   // output batch dims
     int force_split = 0;
+    const uint32_t* pred = nullptr;   // device-side predicate of this form of the GEMM (GemmParams::pred)
+    uint32_t pred_nonzero = 0;
 };
 
 static uint64_t peer_segment_floats(uint64_t n, int world) {
@@ -354,6 +356,16 @@ static int run_peer_exchange(mmeb200_ctx* c, const mmeb200_peer_group* peer, con
     const unsigned blocks = grid_for(n / 4, 256, c->sm_count);
     const unsigned owner_blocks = grid_for(seg / 4, 256, c->sm_count);
     const bool deferred = peer->deferred_output != 0;
+    // The exchange kernels are meant to share the SMs with the next convolution's GEMM, whose CTAs configure the SM for
+    // the largest shared-memory carve-out: blocks of kernels that ask for different carve-outs do not run on an SM together,
+    // so these ask for the same one.
+    static bool carveout_set[64] = {};
+    if (!carveout_set[c->device & 63]) {
+        CUDA_OK(c, cudaFuncSetAttribute(splitk_reduce_peer_scatter_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        CUDA_OK(c, cudaFuncSetAttribute(peer_owner_sum_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        CUDA_OK(c, cudaFuncSetAttribute(peer_result_copy_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        carveout_set[c->device & 63] = true;
+    }
     if (deferred && !c->s_side) {
         CUDA_OK(c, cudaStreamCreateWithFlags(&c->s_side, cudaStreamNonBlocking));
         CUDA_OK(c, cudaEventCreateWithFlags(&c->ev_scatter, cudaEventDisableTiming));
@@ -429,7 +441,8 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     if (tune.raster_gm > 0) p.raster_gm = tune.raster_gm;
     tiles = uint64_t(p.m_tiles) * p.n_tiles * p.batches;
     uint32_t split = 1;
-    if (tune.split_k > 0) j.force_split = tune.split_k;
+    if (j.conv.out_grid) j.force_split = 1;   // the split-K reduction writes rows out_ld apart; a parity class does not
+    else if (tune.split_k > 0) j.force_split = tune.split_k;
     if (j.force_split > 0) split = std::min<uint32_t>(j.force_split, p.num_k_blocks);
     else if (tiles * 2 <= units && p.num_k_blocks >= 32) {
         // worth it only when the k loop is long: the partial sums cost a second kernel and (splits + 1) passes over M x N floats
@@ -455,6 +468,8 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     p.idesc = use_pair ? make_instr_desc(j.a.hw_fmt, j.b.hw_fmt, j.a.mn_major, j.b.mn_major, 256, tile_n)
                        : make_instr_desc(j.a.hw_fmt, j.b.hw_fmt, j.a.mn_major, j.b.mn_major, kBlockM, block_n);
     p.status = c->d_status;
+    p.pred = j.pred;
+    p.pred_nonzero = j.pred_nonzero;
     p.scale = o.scale;
     p.out_dtype = o.dtype;
     p.has_cast = o.has_cast;
@@ -475,6 +490,7 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     void* ws = nullptr;
     const mmeb200_peer_group* peer = c->pending_peer;
     c->pending_peer = nullptr;
+    if (peer && j.pred) return c->fail(MMEB200_ERR_UNSUPPORTED, "the fused dedw exchange takes operands whose fp8 convention the tensor cores share");
     if (peer) {
         // the raw fp32 partial(s) go to scratch; the peer kernels below finish the job
         if (p.batches != 1 || o.has_cast || (uint64_t(j.M) * j.N) % 4)
@@ -500,7 +516,7 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
         p.b_cta_bytes = ((b_cols * elem + kRowBytes - 1) / kRowBytes) * p.block_k * kRowBytes;
     }
     // coalesced TMA stores when the output's base and pitches allow a tensor map
-    if (split == 1 && !peer && tune.tma_store != 0) {
+    if (split == 1 && !peer && tune.tma_store != 0 && !j.conv.out_grid) {
         TmaOperand od;
         od.ptr = o.ptr; od.elem = dtype_size(o.dtype); od.mn_major = false; od.inner = j.N; od.rows = j.M; od.row_stride = o.ld;
         for (int i = 0; i < 3; ++i) { od.bsz[i] = j.bsz[i]; od.bstride[i] = o.bstride[i]; }
@@ -529,6 +545,7 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
         for (int i = 0; i < 3; ++i) { r.out_bstride[i] = o.bstride[i]; r.bsz[i] = j.bsz[i]; }
         r.M = j.M; r.N = j.N; r.batches = p.batches; r.splits = split; r.scale = o.scale; r.cast = o.cast;
         r.rng_philox = o.philox; r.seed = o.seed; r.offset = o.offset;
+        r.pred = j.pred; r.pred_nonzero = j.pred_nonzero;
         const uint64_t total = uint64_t(j.M) * j.N * p.batches;
         const bool vec4 = j.N % 4 == 0 && o.ld % 4 == 0 && o.bstride[0] % 4 == 0 && o.bstride[1] % 4 == 0 && o.bstride[2] % 4 == 0 &&
                           (reinterpret_cast<uintptr_t>(o.ptr) & 15) == 0;
@@ -552,9 +569,11 @@ struct LogicalOperand {
 
 enum PrepKind { PREP_NATIVE, PREP_FP8_TO_BF16, PREP_TF32_ROUND, PREP_SPLIT_A, PREP_SPLIT_B };
 
-static int repack(mmeb200_ctx* c, const LogicalOperand& in, PrepKind kind, TmaOperand* out, uint64_t* k_out) {
+static int repack(mmeb200_ctx* c, const LogicalOperand& in, PrepKind kind, TmaOperand* out, uint64_t* k_out, const uint32_t* pred = nullptr,
+                  uint32_t pred_nonzero = 0) {
     RepackParams r;
     memset(&r, 0, sizeof r);
+    r.pred = pred; r.pred_nonzero = pred_nonzero;
     const int src_elem = dtype_size(in.dtype);
     int dst_elem = src_elem;
     uint64_t segs = 1;
@@ -601,28 +620,32 @@ static int native_operand(const LogicalOperand& in, TmaOperand* out) {
     return 0;
 }
 
-static int fp8_has_foreign_codes(mmeb200_ctx* c, const LogicalOperand& in, const mmeb200_tensor* whole, bool* found) {
-    *found = false;
+// Can any code of this fp8 tensor mean something else to the reference than to the tensor cores? The tensor cores read
+// 1-4-3 in the 'minimal' Inf/NaN convention and 1-5-2 in the 'full' one.
+static bool fp8_may_hold_foreign_codes(const LogicalOperand& in) {
     const int ew = in.dtype == DT_FP8_143 ? 4 : 5;
-    // can any code differ at all?
-    if ((ew == 4 && in.mode == 2) || (ew == 5 && in.mode == 0)) return 0;
+    return !((ew == 4 && in.mode == 2) || (ew == 5 && in.mode == 0));
+}
+// Sets *flag (device memory, zeroed by the caller) when the tensor holds such a code. Stays on the stream: no host round trip.
+static int fp8_scan_foreign_codes(mmeb200_ctx* c, const LogicalOperand& in, const mmeb200_tensor* whole, uint32_t* flag) {
     const uint64_t n = span_elems(whole);
     if (n == 0) return 0;
-    uint32_t* flag = nullptr;
-    TRY(arena_alloc(c, reinterpret_cast<void**>(&flag), 4));
-    CUDA_OK(c, cudaMemsetAsync(flag, 0, 4, c->stream));
-    fp8_scan_kernel<<<grid_for(n, 256, c->sm_count), 256, 0, c->stream>>>(static_cast<const uint8_t*>(whole->data), n, ew, in.mode, flag);
+    fp8_scan_kernel<<<grid_for(n, 256, c->sm_count), 256, 0, c->stream>>>(static_cast<const uint8_t*>(whole->data), n, in.dtype == DT_FP8_143 ? 4 : 5,
+                                                                         in.mode, flag);
     c->launches++;
-    CUDA_OK(c, cudaMemcpyAsync(c->h_status + 1, flag, 4, cudaMemcpyDeviceToHost, c->stream));
-    CUDA_OK(c, cudaStreamSynchronize(c->stream));
-    *found = c->h_status[1] != 0;
+    CUDA_OK(c, cudaGetLastError());
     return 0;
 }
 
 // Decide the tensor-core kind for a dtype pair and turn both logical operands into TMA operands.
+// fp8 operands whose convention the tensor cores may not share get TWO forms: `j` multiplies the codes natively and runs
+// only if a device-side scan found no foreign code; `alt` (then *has_alt) decodes both operands exactly to bf16 first and
+// runs only if the scan found one. Both are enqueued; the flag the scan leaves in device memory decides.
 static int prepare_pair(mmeb200_ctx* c, const LogicalOperand& la, const LogicalOperand& lb, const mmeb200_tensor* ta,
-                        const mmeb200_tensor* tb, GemmJob* j, float* scale) {
+                        const mmeb200_tensor* tb, GemmJob* j, float* scale, GemmJob* alt, float* alt_scale, bool* has_alt) {
     *scale = 1.0f;
+    *alt_scale = 1.0f;
+    *has_alt = false;
     const bool a8 = dtype_is_fp8(la.dtype), b8 = dtype_is_fp8(lb.dtype);
     if (a8 != b8 || (!a8 && la.dtype != lb.dtype))
         return c->fail(MMEB200_ERR_UNSUPPORTED, "operand data types %d and %d cannot be mixed", la.dtype, lb.dtype);
@@ -633,27 +656,35 @@ static int prepare_pair(mmeb200_ctx* c, const LogicalOperand& la, const LogicalO
         if (native_operand(lb, &j->b) != 0 || !tma_compatible(j->b)) TRY(repack(c, lb, PREP_NATIVE, &j->b, &kb));
         j->a.hw_fmt = j->b.hw_fmt = 1;
     } else if (a8) {
-        bool fa = false, fb = false;
-        TRY(fp8_has_foreign_codes(c, la, ta, &fa));
-        TRY(fp8_has_foreign_codes(c, lb, tb, &fb));
-        if (fa || fb) {
-            // some code means Inf/NaN/a number to the reference but not to the tensor cores:
-            // decode both operands exactly to bf16 on the device and multiply those
-            j->kind = KIND_F16;
-            TRY(repack(c, la, PREP_FP8_TO_BF16, &j->a, &ka));
-            TRY(repack(c, lb, PREP_FP8_TO_BF16, &j->b, &kb));
-            j->a.hw_fmt = j->b.hw_fmt = 1;
-        } else {
-            j->kind = KIND_F8;
-            if (native_operand(la, &j->a) != 0 || !tma_compatible(j->a)) TRY(repack(c, la, PREP_NATIVE, &j->a, &ka));
-            if (native_operand(lb, &j->b) != 0 || !tma_compatible(j->b)) TRY(repack(c, lb, PREP_NATIVE, &j->b, &kb));
-            j->a.hw_fmt = la.dtype == DT_FP8_143 ? 0 : 1;
-            j->b.hw_fmt = lb.dtype == DT_FP8_143 ? 0 : 1;
-            // the tensor cores decode 1-4-3 with bias 7 and 1-5-2 with bias 15: fold the difference
-            const int ea = (la.dtype == DT_FP8_143 ? 7 : 15) - la.bias;
-            const int eb = (lb.dtype == DT_FP8_143 ? 7 : 15) - lb.bias;
-            *scale = ldexpf(1.0f, ea + eb);
+        const bool may_a = fp8_may_hold_foreign_codes(la), may_b = fp8_may_hold_foreign_codes(lb);
+        uint32_t* flag = nullptr;
+        if (may_a || may_b) {
+            TRY(arena_alloc(c, reinterpret_cast<void**>(&flag), 4));
+            CUDA_OK(c, cudaMemsetAsync(flag, 0, 4, c->stream));
+            if (may_a) TRY(fp8_scan_foreign_codes(c, la, ta, flag));
+            if (may_b) TRY(fp8_scan_foreign_codes(c, lb, tb, flag));
+            // some code may mean Inf / NaN / another number to the reference than to the tensor cores: the form that decodes
+            // both operands exactly to bf16 on the device and multiplies those runs if the scan raised the flag
+            *alt = *j;
+            alt->kind = KIND_F16;
+            alt->pred = flag; alt->pred_nonzero = 1;
+            uint64_t kda = la.k, kdb = lb.k;
+            TRY(repack(c, la, PREP_FP8_TO_BF16, &alt->a, &kda, flag, 1));
+            TRY(repack(c, lb, PREP_FP8_TO_BF16, &alt->b, &kdb, flag, 1));
+            alt->a.hw_fmt = alt->b.hw_fmt = 1;
+            alt->K = uint32_t(std::max(kda, kdb));
+            *has_alt = true;
+            j->pred = flag; j->pred_nonzero = 0;
         }
+        j->kind = KIND_F8;
+        if (native_operand(la, &j->a) != 0 || !tma_compatible(j->a)) TRY(repack(c, la, PREP_NATIVE, &j->a, &ka, j->pred, 0));
+        if (native_operand(lb, &j->b) != 0 || !tma_compatible(j->b)) TRY(repack(c, lb, PREP_NATIVE, &j->b, &kb, j->pred, 0));
+        j->a.hw_fmt = la.dtype == DT_FP8_143 ? 0 : 1;
+        j->b.hw_fmt = lb.dtype == DT_FP8_143 ? 0 : 1;
+        // the tensor cores decode 1-4-3 with bias 7 and 1-5-2 with bias 15: fold the difference
+        const int ea = (la.dtype == DT_FP8_143 ? 7 : 15) - la.bias;
+        const int eb = (lb.dtype == DT_FP8_143 ? 7 : 15) - lb.bias;
+        *scale = ldexpf(1.0f, ea + eb);
     } else if (la.dtype == DT_TF32) {
         j->kind = KIND_TF32;
         TRY(repack(c, la, PREP_TF32_ROUND, &j->a, &ka));
@@ -830,27 +861,39 @@ static int bgemm_core(mmeb200_ctx* c, const mmeb200_tensor* out, const mmeb200_t
         TRY(run_exact_gemm(c, la, lb, M, N, acc, N, bsz, obs));
         return run_cast(c, out->data, static_cast<uint32_t*>(acc), n, ecs, cast);
     }
-    GemmJob job;
-    float scale = 1.0f;
-    TRY(prepare_pair(c, la, lb, x, w, &job, &scale));
-    job.M = uint32_t(M); job.N = uint32_t(N);
-    if (row_block) job.force_split = 1;
-    for (int i = 0; i < 3; ++i) job.bsz[i] = out->sizes[2 + i];
+    GemmJob job, alt;
+    float scale = 1.0f, alt_scale = 1.0f;
+    bool has_alt = false;
+    TRY(prepare_pair(c, la, lb, x, w, &job, &scale, &alt, &alt_scale, &has_alt));
+    for (GemmJob* g : {&job, &alt}) {
+        g->M = uint32_t(M); g->N = uint32_t(N);
+        if (row_block) g->force_split = 1;
+        for (int i = 0; i < 3; ++i) g->bsz[i] = out->sizes[2 + i];
+    }
 
     OutSpec o;
     memset(&o, 0, sizeof o);
-    o.scale = scale;
     o.ld = out->strides[1];
     for (int i = 0; i < 3; ++i) { o.bsz[i] = out->sizes[2 + i]; o.bstride[i] = out->strides[2 + i]; }
     CastSpec cs;
     TRY(make_cast_spec(c, out, cast, &cs));
     const bool random = cast && cast_needs_random(cs);
     const bool fuse = !cast || !random || cast->rng_kind == MMEB200_RNG_PHILOX || cs.out_dtype == DT_FP32;
+    // both forms of an fp8 GEMM whose operands' convention differs from the tensor cores' are enqueued; the device runs one
+    auto run_forms = [&]() -> int {
+        o.scale = scale;
+        TRY(run_gemm(c, job, o));
+        if (has_alt) {
+            o.scale = alt_scale;
+            TRY(run_gemm(c, alt, o));
+        }
+        return 0;
+    };
     if (fuse) {
         o.ptr = out->data; o.dtype = cs.out_dtype; o.has_cast = cast != nullptr; o.cast = cs;
         o.philox = random && cast->rng_kind == MMEB200_RNG_PHILOX;
         o.seed = cast ? cast->rng_seed : 0; o.offset = (cast ? cast->rng_offset : 0) + rng_extra_offset;
-        TRY(run_gemm(c, job, o));
+        TRY(run_forms());
     } else {
         // LFSR-ordered stochastic rounding needs the reference's sequential element order:
         // accumulate to fp32 scratch, then run the standalone cast
@@ -861,7 +904,7 @@ static int bgemm_core(mmeb200_ctx* c, const mmeb200_tensor* out, const mmeb200_t
         o.ptr = acc; o.dtype = DT_FP32; o.has_cast = false; o.ld = N;
         uint64_t bs = M * N;
         for (int i = 0; i < 3; ++i) { o.bstride[i] = bs; bs *= out->sizes[2 + i]; }
-        TRY(run_gemm(c, job, o));
+        TRY(run_forms());
         TRY(run_cast(c, out->data, static_cast<uint32_t*>(acc), n, cs, cast));
     }
     return 0;
@@ -1193,9 +1236,41 @@ struct ConvShapes {
     uint64_t C, Kout, pixels, taps, rsc;
 };
 
+// One spatial dimension of a parity class of dedx: the dX positions cls, cls + stride, ... and the filter taps that
+// reach them (the taps t with (cls + pad - t * dil) divisible by the stride; RefIm2Col::internalDoCol2Im,
+// mme/mme_reference/im2col.cpp:93-132, visits exactly these).
+struct DedxClassDim {
+    int count;      // dX positions of the class
+    int first_tap, tap_step, taps;
+    int lower;      // dY coordinate that the LAST used tap pairs with the class's first position
+    int dil;        // dY coordinates between consecutive used taps
+};
+static DedxClassDim dedx_class_dim(int cls, int stride, int pad, int dil, int taps, int extent) {
+    DedxClassDim d;
+    memset(&d, 0, sizeof d);
+    d.count = extent > cls ? (extent - cls + stride - 1) / stride : 0;
+    d.first_tap = -1;
+    for (int t = 0; t < taps; ++t)
+        if ((((cls + pad - t * dil) % stride) + stride) % stride == 0) { d.first_tap = t; break; }
+    int g = dil, h = stride;
+    while (h) { const int r = g % h; g = h; h = r; }
+    d.tap_step = stride / g;
+    d.taps = d.first_tap < 0 ? 0 : (taps - 1 - d.first_tap) / d.tap_step + 1;
+    if (d.taps) {
+        const int last = d.first_tap + (d.taps - 1) * d.tap_step;
+        d.lower = (cls + pad - last * dil) / stride;     // exact
+        d.dil = dil * d.tap_step / stride;
+    }
+    return d;
+}
+
+// cls_w / cls_h: dedx of a strided convolution is planned one parity class of dX positions at a time (0, 0 and nothing
+// else for stride 1); *cls_empty: no tap reaches the class (its positions stay zero).
 static int conv_fast_path(mmeb200_ctx* c, const mmeb200_tensor* x, const mmeb200_tensor* w, const mmeb200_tensor* y,
-                          const mmeb200_conv_params* p, int op, GemmJob* job, float* scale, bool* taken) {
+                          const mmeb200_conv_params* p, int op, GemmJob* job, float* scale, bool* taken, int cls_w = 0, int cls_h = 0,
+                          bool* cls_empty = nullptr) {
     *taken = false;
+    if (cls_empty) *cls_empty = false;
     const mmeb200_tensor* act = (op == MMEB200_OP_DEDX) ? y : x;   // tensor read through im2col TMA
     const mmeb200_tensor* other = (op == MMEB200_OP_DEDW) ? y : w; // the plain (tiled) operand
     if (p->dim != 2 || x->dims != 4 || y->dims != 4 || w->dims != 4) return 0;
@@ -1255,19 +1330,36 @@ static int conv_fast_path(mmeb200_ctx* c, const mmeb200_tensor* x, const mmeb200
         job->b.ptr = w->data; job->b.elem = elem; job->b.mn_major = true; job->b.inner = Kout; job->b.rows = uint64_t(S) * R * C; job->b.row_stride = Kout;
         job->a.mn_major = false;
     } else if (op == MMEB200_OP_DEDX) {
-        if (p->stride[0] != 1 || p->stride[1] != 1) return 0;
         if (Kout % block_k) return 0;
-        g.out_w = W; g.out_h = H; g.stride_w = 1; g.stride_h = 1;
-        g.lower_w = p->padding[0] - (int(S) - 1) * p->dilation[0];
-        g.lower_h = p->padding[1] - (int(R) - 1) * p->dilation[1];
+        const DedxClassDim dw_ = dedx_class_dim(cls_w, p->stride[0], p->padding[0], p->dilation[0], int(S), int(W));
+        const DedxClassDim dh_ = dedx_class_dim(cls_h, p->stride[1], p->padding[1], p->dilation[1], int(R), int(H));
+        if (dw_.count == 0 || dh_.count == 0 || dw_.taps == 0 || dh_.taps == 0) {
+            if (cls_empty) *cls_empty = true;
+            *taken = true;
+            return 0;
+        }
+        g.out_w = dw_.count; g.out_h = dh_.count; g.stride_w = 1; g.stride_h = 1;
+        g.lower_w = dw_.lower; g.lower_h = dh_.lower;
+        g.dil_w = dw_.dil; g.dil_h = dh_.dil;
+        g.taps_w = dw_.taps; g.taps_h = dh_.taps;
         lower[0] = g.lower_w; lower[1] = g.lower_h;
-        upper[0] = int(W) - int(Wo) + g.lower_w;
-        upper[1] = int(H) - int(Ho) + g.lower_h;
+        upper[0] = dw_.count - int(Wo) + g.lower_w;
+        upper[1] = dh_.count - int(Ho) + g.lower_h;
         g.flip = 1;
         g.channels = Kout; g.k_blocks_per_tap = Kout / block_k;
-        g.b_tap_local = 1; g.b_tap_rows = C;
+        g.b_tap_local = 1;
+        g.b_tap_rows = dw_.tap_step * int(C);
+        g.b_tap_rows_r = dh_.tap_step * int(S) * int(C);
+        g.b_row0 = (dh_.first_tap * int(S) + dw_.first_tap) * int(C);
+        if (p->stride[0] != 1 || p->stride[1] != 1) {
+            g.out_grid = 1;
+            g.out_base = (int64_t(cls_h) * W + cls_w) * C;
+            g.out_stride_w = int64_t(p->stride[0]) * C;
+            g.out_stride_h = int64_t(p->stride[1]) * W * C;
+            g.out_stride_n = int64_t(H) * W * C;
+        }
         chan_box = block_k; pix_box = kBlockM;
-        job->M = W * H * B; job->N = C; job->K = S * R * Kout;
+        job->M = uint32_t(dw_.count) * uint32_t(dh_.count) * B; job->N = C; job->K = uint32_t(dw_.taps * dh_.taps) * Kout;
         // B = W viewed as [RSC rows x Kout], K (=Kout) contiguous: row tap*C + c
         job->b.ptr = w->data; job->b.elem = elem; job->b.mn_major = false; job->b.inner = Kout; job->b.rows = uint64_t(S) * R * C; job->b.row_stride = Kout;
         if ((Kout * elem) % 16) return 0;
@@ -1405,7 +1497,8 @@ int mmeb200_conv(mmeb200_ctx* c, mmeb200_tensor* out, const mmeb200_tensor* x, c
     bool fast = false;
     const bool dense_out = is_dense(out);
     const bool exact = c->acc_mode == MMEB200_ACC_CHIP_EXACT;
-    if (dense_out && !exact && !(op == MMEB200_OP_DEDX && rounding != RM_NE))
+    const bool strided_dedx = op == MMEB200_OP_DEDX && p->dim == 2 && (p->stride[0] != 1 || p->stride[1] != 1);
+    if (dense_out && !exact && !(op == MMEB200_OP_DEDX && rounding != RM_NE) && !strided_dedx)
         TRY(conv_fast_path(c, &sx.t, &sw.t, &sy.t, p, op, &job, &scale, &fast));
     if (fast) {
         o.scale = scale;
@@ -1419,7 +1512,37 @@ int mmeb200_conv(mmeb200_ctx* c, mmeb200_tensor* out, const mmeb200_tensor* x, c
         TRY(stage_out(c, &so));
         return finish_call(c, any_host);
     }
-
+    // ---- dedx of a strided convolution as implicit GEMMs: the dX positions fall into stride_w x stride_h parity classes,
+    //      each reached by its own subset of the taps (im2col.cpp:93-132 adds a tap only where the position divides);
+    //      one launch per class reads dY through im2col-mode TMA and stores straight into the class's sub-grid of dX.
+    //      No column matrix is materialised.
+    if (strided_dedx && dense_out && !exact && rounding == RM_NE && p->stride[0] <= 8 && p->stride[1] <= 8) {
+        std::vector<GemmJob> jobs;
+        bool all = true, any_empty = false;
+        float cls_scale = 1.0f;
+        for (int ch = 0; ch < p->stride[1] && all; ++ch)
+            for (int cw = 0; cw < p->stride[0] && all; ++cw) {
+                GemmJob cj;
+                bool taken = false, empty = false;
+                TRY(conv_fast_path(c, &sx.t, &sw.t, &sy.t, p, op, &cj, &cls_scale, &taken, cw, ch, &empty));
+                all = taken;
+                any_empty |= empty;
+                if (taken && !empty) jobs.push_back(cj);
+            }
+        if (all) {
+            o.scale = cls_scale;
+            if (lfsr_cast) {
+                TRY(arena_alloc(c, &acc, n_out * 4));
+                o.ptr = acc; o.dtype = DT_FP32; o.has_cast = false; o.ld = C;
+            } else fused_out(C);
+            // positions that no tap reaches keep the zero the reference fills dX with (im2col.cpp:106)
+            if (any_empty) CUDA_OK(c, cudaMemsetAsync(o.ptr, 0, n_out * dtype_size(o.dtype), c->stream));
+            for (GemmJob& cj : jobs) TRY(run_gemm(c, cj, o));
+            if (lfsr_cast) TRY(run_cast(c, so.t.data, static_cast<uint32_t*>(acc), n_out, cs, cast));
+            TRY(stage_out(c, &so));
+            return finish_call(c, any_host);
+        }
+    }
     // ---- general lowering: materialised im2col (fwd, dedw) / col2im (dedx) around the same GEMM
     const mmeb200_tensor* act = (op == MMEB200_OP_DEDX) ? &so.t : &sx.t;  // tensor with the (C,W,H,D,B) geometry
     ConvLowerParams lp;
@@ -1468,13 +1591,25 @@ int mmeb200_conv(mmeb200_ctx* c, mmeb200_tensor* out, const mmeb200_tensor* x, c
     }
     mmeb200_tensor ta_whole = (op == MMEB200_OP_DEDX) ? sy.t : sx.t;
     mmeb200_tensor tb_whole = (op == MMEB200_OP_DEDW) ? sy.t : sw.t;
-    GemmJob gj;
+    GemmJob gj, gj_alt;
+    float alt_scale = 1.0f;
+    bool has_alt = false;
     const uint32_t one3[3] = {1, 1, 1};
     const uint64_t zero3[3] = {0, 0, 0};
     if (!exact) {
-        TRY(prepare_pair(c, la, lb, &ta_whole, &tb_whole, &gj, &scale));
-        gj.M = uint32_t(M); gj.N = uint32_t(N);
+        TRY(prepare_pair(c, la, lb, &ta_whole, &tb_whole, &gj, &scale, &gj_alt, &alt_scale, &has_alt));
+        gj.M = gj_alt.M = uint32_t(M); gj.N = gj_alt.N = uint32_t(N);
     }
+    // both forms of an fp8 GEMM whose operands' convention differs from the tensor cores' are enqueued; the device runs one
+    auto run_forms = [&]() -> int {
+        o.scale = scale;
+        TRY(run_gemm(c, gj, o));
+        if (has_alt) {
+            o.scale = alt_scale;
+            TRY(run_gemm(c, gj_alt, o));
+        }
+        return 0;
+    };
     o.scale = scale;
     if (op == MMEB200_OP_DEDX) {
         // GEMM -> fp32 [pixels x RSC] -> col2im (fp32 dx) -> optional cast
@@ -1482,7 +1617,7 @@ int mmeb200_conv(mmeb200_ctx* c, mmeb200_tensor* out, const mmeb200_tensor* x, c
         TRY(arena_alloc(c, &cm, M * N * 4));
         o.ptr = cm; o.dtype = DT_FP32; o.has_cast = false; o.ld = N;
         if (exact) TRY(run_exact_gemm(c, la, lb, M, N, cm, N, one3, zero3));
-        else TRY(run_gemm(c, gj, o));
+        else TRY(run_forms());
         lp.ld = N;
         float* dx = nullptr;
         uint64_t dx_span = span_elems(out);
@@ -1526,11 +1661,11 @@ int mmeb200_conv(mmeb200_ctx* c, mmeb200_tensor* out, const mmeb200_tensor* x, c
         } else if (lfsr_cast) {
             TRY(arena_alloc(c, &acc, n_out * 4));
             o.ptr = acc; o.dtype = DT_FP32; o.has_cast = false; o.ld = N;
-            TRY(run_gemm(c, gj, o));
+            TRY(run_forms());
             TRY(run_cast(c, so.t.data, static_cast<uint32_t*>(acc), n_out, cs, cast));
         } else {
             fused_out(ld);
-            TRY(run_gemm(c, gj, o));
+            TRY(run_forms());
         }
     }
     TRY(stage_out(c, &so));

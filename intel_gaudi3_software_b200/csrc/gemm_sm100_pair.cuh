@@ -48,6 +48,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<EPI_GROUPS>
     gemm_tcgen05_pair_kernel(const __grid_constant__ GemmParams p) {
     using S = PairSmem<EPI_GROUPS>;
     constexpr int STAGES = S::kStages;
+    if (launch_is_predicated_off(p.pred, p.pred_nonzero)) return;   // uniform over the grid (both CTAs of every pair)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * S::kStageBytes);

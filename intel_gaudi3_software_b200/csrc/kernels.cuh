@@ -206,6 +206,8 @@ struct RepackParams {
     uint64_t dst_ld;           // elements per dst row (all segments)
     uint64_t seg;              // elements per segment (k rounded up), modes 3/4
     int mode, src_elem, dtype, bias, inf_nan;
+    const uint32_t* pred;      // see GemmParams::pred
+    uint32_t pred_nonzero;
 };
 
 __device__ __forceinline__ uint32_t tf32_rne(uint32_t x) {
@@ -215,6 +217,7 @@ __device__ __forceinline__ uint32_t tf32_rne(uint32_t x) {
 }
 
 __global__ void repack_kernel(RepackParams p) {
+    if (p.pred != nullptr && ((*p.pred != 0u) != (p.pred_nonzero != 0u))) return;
     const uint64_t per_batch = p.rows * p.k;
     const uint64_t batches = uint64_t(p.bsz[0]) * p.bsz[1] * p.bsz[2];
     const uint64_t total = per_batch * batches;
@@ -356,9 +359,12 @@ struct ReduceOut {
     CastSpec cast;
     uint32_t rng_philox;
     uint64_t seed, offset;
+    const uint32_t* pred;      // see GemmParams::pred
+    uint32_t pred_nonzero;
 };
 
 __global__ void splitk_reduce_kernel(const float* __restrict__ ws, ReduceOut r) {
+    if (r.pred != nullptr && ((*r.pred != 0u) != (r.pred_nonzero != 0u))) return;
     const uint64_t per = uint64_t(r.M) * r.N;
     const uint64_t total = per * r.batches;
     const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
@@ -385,6 +391,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, ReduceOut r) 
 // Four consecutive columns per thread (one 16-byte load per split, one vector store): for outputs whose
 // row length, pitches and base allow it. Same summation order as the scalar kernel, so the same bits.
 __global__ void splitk_reduce_vec4_kernel(const float* __restrict__ ws, ReduceOut r) {
+    if (r.pred != nullptr && ((*r.pred != 0u) != (r.pred_nonzero != 0u))) return;
     const uint64_t per = uint64_t(r.M) * r.N;
     const uint64_t total = per * r.batches;
     const uint64_t total4 = total / 4;

@@ -151,6 +151,41 @@ def test_resnet_conv_full_size(calc, best_oracle, port, opname):
         b.free()
 
 
+def test_resnet_dedx_stride2_full_size(calc, best_oracle, port):
+    """dedx of the 3x3 stride-2 convolution at the ResNet shape (dX 64 x 56 x 56 x 256, dY 64 x 28 x 28 x 256): four implicit
+    GEMMs, one per parity class of dX positions, no column matrix (the lowering the reference uses would materialise
+    50176 x 2304 fp32 values). Whole first and last image against the oracle, fp32 accumulators and the fused bf16 output."""
+    wl = bench.WORKLOADS["conv_dedx_stride2"]
+    xs, ws, ys = bench.conv_shapes(wl)
+    xb, wb, yb = bench.synth_inputs(wl, seed=4)
+    cp = abi.make_conv_params(2, (1, 1), (2, 2), (1, 1))
+    n_out = int(np.prod(xs))
+    dx, dw, dy = calc.to_device(xb), calc.to_device(wb), calc.to_device(yb)
+    do, do16 = calc.alloc(n_out * 4), calc.alloc(n_out * 2)
+    tens = (T(dx.ptr, abi.BF16, xs, mem_space=1), T(dw.ptr, abi.BF16, ws, mem_space=1), T(dy.ptr, abi.BF16, ys, mem_space=1))
+    before = calc.launch_count()
+    calc.do_convolution(T(do.ptr, abi.FP32, xs, mem_space=1), *tens, cp, abi.OP_DEDX)
+    assert calc.launch_count() - before == 4
+    calc.do_convolution(T(do16.ptr, abi.BF16, xs, mem_space=1), *tens, cp, abi.OP_DEDX, abi.RM_NE, abi.make_cast_params(abi.RM_NE))
+    calc.sync(20_000_000_000)
+    out, out16 = do.download(np.float32), do16.download(np.uint16)
+    img_x, img_y = int(np.prod(xs[:3])), int(np.prod(ys[:3]))
+    xs1, ys1 = xs[:3] + [1], ys[:3] + [1]
+    for img in (0, xs[3] - 1):
+        yi = yb[img * img_y:(img + 1) * img_y]
+        xi = xb[img * img_x:(img + 1) * img_x]
+        r = np.zeros(img_x, np.float32)
+        assert best_oracle.conv(T(r, abi.FP32, xs1), T(xi, abi.BF16, xs1), T(wb, abi.BF16, ws), T(yi, abi.BF16, ys1), cp, abi.OP_DEDX) == 0
+        sabs = util.conv_sum_abs(best_oracle, (xs1, ws, ys1), (xi, wb, yi), abi.BF16, cp, abi.OP_DEDX)
+        got = out[img * img_x:(img + 1) * img_x]
+        util.assert_acc(got, r, sabs, "stride-2 dedx image %d" % img)
+        got16, ref16 = out16[img * img_x:(img + 1) * img_x], port.fp32_to_bf16(r)
+        inexact, far = util.check_rounded(got16, ref16, 16, util.bf16_to_f32(got16), util.bf16_to_f32(ref16), sabs, "stride-2 dedx bf16 image %d" % img)
+        assert inexact <= 0.02 * img_x
+    for b in (dx, dw, dy, do, do16):
+        b.free()
+
+
 def test_batched_attention_gemm(calc, best_oracle, port):
     """The attention-shaped batch: 64 x ([4096 x 128] . [128 x 4096]^T-style abt) fp8_143 -> bf16. K = 128 sums of fp8
     products are exact in fp32, so rounded outputs are compared bit for bit on sampled batches."""

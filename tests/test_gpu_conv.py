@@ -64,6 +64,34 @@ def test_implicit_gemm_path(calc, best_oracle, c):
     check_all_ops(calc, best_oracle, c, seed=1)
 
 
+@pytest.mark.parametrize("c", [
+    (64, 128, 33, 31, 2, 3, 2, (2, 2), (1, 1), (1, 1)),      # 2 x 2 parity classes with 2/1 x 1/1 taps
+    (64, 64, 40, 36, 2, 3, 3, (2, 2), (1, 1), (1, 1)),       # the ResNet down-sampling geometry
+    (128, 64, 41, 37, 2, 5, 5, (3, 2), (2, 2), (2, 1)),      # stride 3 x 2 with dilation 2 x 1: some classes see no tap in one dim
+    (64, 256, 48, 44, 2, 1, 1, (2, 2), (0, 0), (1, 1)),      # 1 x 1 filter: three of the four classes stay zero
+    (64, 64, 39, 35, 3, 4, 3, (2, 3), (0, 1), (1, 2)),       # odd extents: the last dX rows lie beyond the last tap
+])
+def test_strided_dedx_runs_as_implicit_gemm_per_parity_class(calc, best_oracle, c):
+    """dedx of a strided convolution on the implicit-GEMM path (one launch per parity class of dX positions, no column
+    matrix): every output against the oracle, positions no tap reaches included (they must be zero)."""
+    rng = np.random.default_rng(11)
+    shapes, (x, w, y), bits = make_inputs(rng, c)
+    xs, ws, ys = shapes
+    cp = abi.make_conv_params(2, c[8], c[7], c[9])
+    o1, o2 = np.full(int(np.prod(xs)), 3.0, np.float32), np.full(int(np.prod(xs)), 3.0, np.float32)
+    before = calc.launch_count()
+    calc.do_convolution(T(o1, abi.FP32, xs), x, w, y, cp, abi.OP_DEDX)
+    launches = calc.launch_count() - before
+    assert launches <= c[7][0] * c[7][1], launches      # at most one GEMM per class: no im2col / col2im kernels ran
+    assert best_oracle.conv(T(o2, abi.FP32, xs), x, w, y, cp, abi.OP_DEDX) == 0
+    util.assert_acc(o1, o2, util.conv_sum_abs(best_oracle, shapes, bits, abi.BF16, cp, abi.OP_DEDX), "strided dedx %s" % (c,))
+    assert ((o2 == 0) <= (o1 == 0)).all()                # where the reference left its zero fill, so did we
+    # the fused bf16 cast writes the same sub-grids
+    o16 = np.full(int(np.prod(xs)), 0x1234, np.uint16)
+    calc.do_convolution(T(o16, abi.BF16, xs), x, w, y, cp, abi.OP_DEDX, abi.RM_NE, abi.make_cast_params(abi.RM_NE))
+    assert (o16 == util.f32_to_bf16_rne(o1)).all()
+
+
 @pytest.mark.parametrize("pair", [1, 0])
 def test_implicit_gemm_wide_channels_on_both_kernels(calc, best_oracle, pair):
     """256 channels in and out: all three operations qualify for the CTA-pair kernel (pair = 1); pair = 0 forces

@@ -167,6 +167,54 @@ def test_fp8_all_formats_biases_and_infnan_modes(calc, best_oracle, port, tx, tw
         assert err <= util.ACC_TOL, (tame, err)
 
 
+def test_foreign_code_decision_stays_on_the_device(calc, best_oracle, port):
+    """fp8_143 in the reference's default 'full' Inf/NaN convention holds codes (0x78 ...) that the tensor cores would read
+    as numbers. Whether a tensor holds one is found by a scan ON the stream, and both forms of the GEMM are enqueued behind
+    it: a call on device tensors must return while work enqueued before it is still running (no host round trip), and both
+    outcomes must match the oracle."""
+    import time
+    rng = np.random.default_rng(77)
+    M, N, K = 512, 512, 512
+    kw = dict(fp_bias=7, inf_nan_mode=abi.INFNAN_FULL)
+    clean = (rng.integers(0, 256, M * K).astype(np.uint8) & 0xBF, rng.integers(0, 256, K * N).astype(np.uint8) & 0xBF)
+    dirty = (clean[0].copy(), clean[1].copy())
+    dirty[0][12345] = 0x78          # +Inf in this convention, 256 to the tensor cores
+    dirty[1][54321] = 0x7D          # NaN in this convention
+    # long-running work on the same stream: a bit-exact GEMM on the CUDA cores
+    big = 3072
+    bx, bw, bo = calc.to_device(rng.integers(0, 120, big * big).astype(np.uint8)), calc.to_device(rng.integers(0, 120, big * big).astype(np.uint8)), calc.alloc(big * big * 4)
+    kn = dict(fp_bias=7, inf_nan_mode=abi.INFNAN_MINIMAL, mem_space=abi.MEM_DEVICE)
+    for xa, wa in (clean, dirty):
+        dx, dw, do = calc.to_device(xa), calc.to_device(wa), calc.alloc(M * N * 4)
+        calc.sync()
+        calc.set_accumulation(abi.ACC_CHIP_EXACT)
+        try:
+            t0 = time.perf_counter()
+            calc.do_batch_gemm(T(bo.ptr, abi.FP32, [big, big], mem_space=abi.MEM_DEVICE), T(bx.ptr, abi.FP8_143, [big, big], **kn),
+                               T(bw.ptr, abi.FP8_143, [big, big], **kn), abi.OP_AB)
+        finally:
+            calc.set_accumulation(abi.ACC_TENSOR_CORE)
+        calc.do_batch_gemm(T(do.ptr, abi.FP32, [N, M], mem_space=abi.MEM_DEVICE), T(dx.ptr, abi.FP8_143, [K, M], mem_space=abi.MEM_DEVICE, **kw),
+                           T(dw.ptr, abi.FP8_143, [N, K], mem_space=abi.MEM_DEVICE, **kw), abi.OP_AB)
+        t_enqueued = time.perf_counter() - t0
+        calc.sync(30_000_000_000)
+        t_done = time.perf_counter() - t0
+        assert t_done > 0.02 and t_enqueued < 0.5 * t_done, (t_enqueued, t_done)   # the call came back long before the stream drained
+        o = do.download(np.float32)
+        r = np.zeros(M * N, np.float32)
+        assert best_oracle.bgemm(T(r, abi.FP32, [N, M]), T(xa, abi.FP8_143, [K, M], **kw), T(wa, abi.FP8_143, [N, K], **kw), abi.OP_AB) == 0
+        assert (np.isnan(o) == np.isnan(r)).all() and (np.isinf(o) == np.isinf(r)).all()
+        fin = np.isfinite(r)
+        xf, wf = util.decode(xa, abi.FP8_143, 7, 0, port).reshape(M, K), util.decode(wa, abi.FP8_143, 7, 0, port).reshape(K, N)
+        sabs = np.abs(np.nan_to_num(xf, nan=0, posinf=0, neginf=0)).astype(np.float64) @ np.abs(np.nan_to_num(wf, nan=0, posinf=0, neginf=0)).astype(np.float64)
+        assert util.acc_error(np.where(fin, o, 0).reshape(M, N), np.where(fin, r, 0).reshape(M, N), sabs) <= util.ACC_TOL
+        for b in (dx, dw, do):
+            b.free()
+    assert np.isnan(o).any() and np.isinf(o).any()      # the second pass did go through the decoded form
+    for b in (bx, bw, bo):
+        b.free()
+
+
 def test_fp8_same_type_is_bit_identical_to_the_reference_model(calc, best_oracle, port):
     """fp8 x fp8 products are exact in fp32 and short sums stay exact: for in-range values the
     tensor-core accumulation and the reference's tree agree bit for bit at K = 128 (the attention-shaped batch)."""
