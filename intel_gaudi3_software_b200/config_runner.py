@@ -46,9 +46,10 @@ REDUCTION_OPS = {"add": 0, "sub": 1, "min": 2, "max": 3, "max_0": 4, "none": 5}
 REDUCTION_RM = {"rn": 0, "rz": 1, "ru": 2, "rd": 3}
 INF_NAN = {"fullInfNan": 0, "noInfNan": 1, "minInfNan": 2}
 SHAPE_KEYS = ("xSizes", "wSizes", "ySizes", "xStrides", "wStrides", "yStrides", "dilation", "strides", "padding",
-              "xSizes2", "wSizes2")   # the second size set shapes the mask operands of a masked bgemm
-# shape-like keys of features the backend does not model (second GEMM of a dual-GEMM descriptor, recipe tests)
-IGNORED_LIST_KEYS = ("ySizes2", "xStrides2", "wStrides2", "yStrides2", "recipeTest", "optimizationTest")
+              "xSizes2", "wSizes2", "ySizes2", "xStrides2", "wStrides2", "yStrides2")
+# the second set shapes the mask operands of a masked bgemm, or the second GEMM of a dual-GEMM test
+# shape-like keys of features the backend does not model (recipe tests)
+IGNORED_LIST_KEYS = ("recipeTest", "optimizationTest")
 BOOL_KEYS = ("reluEn", "clippingEn", "clipInfIn", "flushDenormals", "stochasticFlush", "memsetOutput", "memsetVoidPixels",
              "maskedBgemm", "skipTest", "skipRef", "dualGemm")
 NUM_KEYS = ("xMean", "wMean", "yMean", "xStd", "wStd", "yStd", "xMinVal", "wMinVal", "yMinVal", "xMaxVal", "wMaxVal", "yMaxVal")
@@ -64,7 +65,8 @@ def default_test():
     t = {"testName": "", "operation": None, "inTypeFloat": None, "in2TypeFloat": None, "outTypeFloat": None,
          "conversionRoundingMode": 0, "reductionOp": REDUCTION_OPS["none"], "reductionRm": 0,
          "infNanModeA": 0, "infNanModeB": 0, "infNanModeOut": 0, "fp8BiasIn": 15, "fp8BiasIn2": None, "fp8BiasOut": 15,
-         "xSizes": [0] * 5, "wSizes": [0] * 5, "ySizes": [0] * 5, "xSizes2": [0] * 5, "wSizes2": [0] * 5, "xStrides": [0] * 5, "wStrides": [0] * 5, "yStrides": [0] * 5,
+         "xSizes": [0] * 5, "wSizes": [0] * 5, "ySizes": [0] * 5, "xSizes2": [0] * 5, "wSizes2": [0] * 5, "ySizes2": [0] * 5,
+         "xStrides": [0] * 5, "wStrides": [0] * 5, "yStrides": [0] * 5, "xStrides2": [0] * 5, "wStrides2": [0] * 5, "yStrides2": [0] * 5,
          "padding": [0, 0, 0], "dilation": [1, 1, 1], "strides": [1, 1, 1],
          "xMean": 0.0, "wMean": 0.0, "yMean": 0.0, "xStd": 0.0, "wStd": 0.0, "yStd": 0.0,
          "xMinVal": -1.0, "wMinVal": -1.0, "yMinVal": -1.0, "xMaxVal": 10.0, "wMaxVal": 10.0, "yMaxVal": 10.0,
@@ -157,8 +159,18 @@ class Parser:
                 # last key varies fastest, as in makeCartesianProductTests
                 for combo in itertools.product(*value_lists):
                     parsed = self._configure(keys, combo, self.seed + len(out))
-                    if parsed is not None:
-                        out.append(parsed)
+                    if parsed is None:
+                        continue
+                    out.append(parsed)
+                    if parsed["dualGemm"]:
+                        # a dual-GEMM descriptor holds two independent GEMMs; the calculator runs them one after the other
+                        # (the loop over tensorParams in mme_test_manager.cpp:799), so the second becomes a test of its own
+                        second = dict(parsed, dualGemm=False, seed=parsed["seed"] + 7919, testName=parsed["testName"] + " (second gemm)")
+                        for role in ("x", "w", "y"):
+                            second[role + "Sizes"] = [max(1, v) for v in parsed[role + "Sizes2"]]
+                            second[role + "Strides"] = list(parsed[role + "Strides2"])
+                        parsed["dualGemm"] = False
+                        out.append(second)
         return out
 
     # ---- one test ------------------------------------------------------------------------------------
@@ -337,7 +349,10 @@ def common_dim_size(t):
 
 
 class TestTensors:
-    """Host arrays of one test: x, w, y (the output role holds its initial contents), plus the mask pair."""
+    """Host arrays of one test: x, w, y (the output role holds its initial contents), plus the mask pair.
+
+    A role with explicit element strides (xStrides / wStrides / yStrides, mme_test_data_gen.cpp:222-298) owns a buffer as
+    long as the strides span; the generated values sit at the strided positions and the gaps hold zeros."""
 
     def __init__(self, t, calc):
         self.t = t
@@ -352,7 +367,7 @@ class TestTensors:
                 # outputs start at 0 when the test asks for it (dedx always), else at the largest float
                 zero = t["memsetOutput"] or (t["operation"] in (abi.OP_DEDX, abi.OP_TRANSPOSED_DEDX) and not t["memsetVoidPixels"])
                 v = 0.0 if zero else float(np.finfo(np.float32).max)
-                self.host[role] = self._generate(calc, role, n, seed + k, constant=v)
+                self.host[role] = self._place(role, self._generate(calc, role, n, seed + k, constant=v))
             elif role == "w" and t["operation"] in DMA_OPS:
                 continue
             elif role == "x" and t["operation"] == abi.OP_REDUCTION_ADD:
@@ -363,11 +378,56 @@ class TestTensors:
                               packing=t["packingFactor"], level=t["reductionLevel"])
                 self.host[role] = out
             else:
-                self.host[role] = self._generate(calc, role, n, seed + k)
+                self.host[role] = self._place(role, self._generate(calc, role, n, seed + k))
         if t["maskedBgemm"]:
             for k, (role, key) in enumerate((("x", "xSizes2"), ("w", "wSizes2"))):
                 n = int(np.prod([max(1, v) for v in t[key]]))
                 self.host[role + "Mask"] = self._generate(calc, role, n, seed + 8 + k)
+
+    # ---- strides -------------------------------------------------------------------------------------
+    def strides(self, role):
+        """Element strides of a role (fastest dimension first), or None for a dense tensor."""
+        st = self.t.get(role + "Strides")
+        if not st or not any(st):
+            return None
+        sizes = [max(1, v) for v in self.t[role + "Sizes"]]
+        st = list(st) + [0] * (5 - len(st))
+        dense, acc = [], 1
+        for n in sizes:
+            dense.append(acc)
+            acc *= n
+        if st[0] != 1:
+            raise ConfigError("%sStrides: the fastest dimension must have stride 1" % role)
+        # a zero entry keeps the dense value of that dimension
+        st = [s if s else d for s, d in zip(st, dense)]
+        return None if st == dense else st
+
+    def span(self, role):
+        sizes = [max(1, v) for v in self.t[role + "Sizes"]]
+        st = self.strides(role)
+        if st is None:
+            return int(np.prod(sizes))
+        return 1 + sum((n - 1) * s for n, s in zip(sizes, st))
+
+    def _view(self, role, array):
+        """The logical elements of a role inside its (strided) buffer, as an array indexed [d4][d3][d2][d1][d0]."""
+        sizes = [max(1, v) for v in self.t[role + "Sizes"]]
+        st = self.strides(role)
+        item = array.dtype.itemsize
+        return np.lib.stride_tricks.as_strided(array, shape=sizes[::-1], strides=[s * item for s in st[::-1]], writeable=True)
+
+    def _place(self, role, dense):
+        if self.strides(role) is None:
+            return dense
+        buf = np.zeros(self.span(role), dense.dtype)
+        self._view(role, buf)[...] = dense.reshape([max(1, v) for v in self.t[role + "Sizes"]][::-1])
+        return buf
+
+    def logical(self, role, array):
+        """The logical elements of `array` (a buffer laid out like `role`) as a dense 1-D array."""
+        if self.strides(role) is None:
+            return array
+        return np.ascontiguousarray(self._view(role, array)).reshape(-1)
 
     def _generate(self, calc, role, n, seed, constant=None):
         """DataGenerator::fillTensorData (mme_test_data_gen.cpp:783-817) on the device: a constant when min == max (or for
@@ -389,33 +449,38 @@ class TestTensors:
             calc.generate(tensor, abi.GEN_UNIFORM, lo, hi, seed=seed)
         return out
 
-    def tensor(self, role, array=None, sizes_key=None, dtype=None):
+    def tensor(self, role, array=None, sizes_key=None, dtype=None, flat=False):
+        """Descriptor of a role's tensor over `array` (default: the role's own buffer). dtype: the same geometry with another
+        element type (the fp32 accumulator); flat: the whole buffer, gaps included, as a dense 1-D tensor (doActivation and
+        doMemoryWrite walk memory, not coordinates)."""
         base = role.replace("Mask", "")
         dt, bias, mode = self.attr[base]
         if dtype is not None:
             dt, bias, mode = dtype, 0, abi.INFNAN_FULL
+        data = self.host[role] if array is None else array
+        if flat:
+            return T(data, dt, [data.size], fp_bias=bias, inf_nan_mode=mode)
         sizes = self.t[sizes_key or (base + "Sizes")]
         sizes = [max(1, v) for v in sizes]
-        strides = self.t.get(base + "Strides") if sizes_key is None and dtype is None else None
-        if strides and any(strides):
-            raise ConfigError("strided test tensors are not generated by this runner; give dense sizes")
-        return T(self.host[role] if array is None else array, dt, sizes, fp_bias=bias, inf_nan_mode=mode)
+        strides = self.strides(base) if sizes_key is None else None
+        return T(data, dt, sizes, strides=strides, fp_bias=bias, inf_nan_mode=mode)
 
 
-def run_test(calc, t, tensors=None):
-    """One test on the backend; returns (output array in its dtype, TestTensors)."""
-    tt = tensors or TestTensors(t, calc)
+def run_flow(calc, t, tt):
+    """MmeTestManager::runReference (mme_test_manager.cpp:766-905) with `calc` as the calculator: anything that has the
+    calculator's methods (the B200 backend, or a CPU checker wrapped to the same names). Returns the output buffer in its
+    own layout (strided roles keep their gaps)."""
     op = t["operation"]
     out_role = tt.out_role
     out_dtype, out_bias, out_mode = tt.attr[out_role]
+    n_span = tt.span(out_role)
     n_out = int(np.prod(t[out_role + "Sizes"]))
     clip = t["clippingEn"] or t["conversionRoundingMode"] in (abi.RM_SR, abi.RM_SR_NE_DNORM)   # clipEn || usesLfsr
-    mme_out = np.zeros(n_out, abi.NP_DTYPE[out_dtype])
-    mme_out_t = tt.tensor(out_role, mme_out)
+    mme_out = np.zeros(n_span, abi.NP_DTYPE[out_dtype])
     if op in DMA_OPS:
-        calc.do_dma(mme_out_t, tt.tensor("x"), op)
+        calc.do_dma(tt.tensor(out_role, mme_out), tt.tensor("x"), op)
     else:
-        acc = np.zeros(n_out, np.float32)
+        acc = np.zeros(n_span, np.float32)
         acc_t = tt.tensor(out_role, acc, dtype=abi.FP32)
         if op in CONV_OPS:
             params = abi.make_conv_params(3, t["padding"], t["strides"], t["dilation"], relu=False)
@@ -433,16 +498,22 @@ def run_test(calc, t, tensors=None):
         else:
             calc.do_batch_gemm(acc_t, tt.tensor("x"), tt.tensor("w"), op)
         if t["maskedBgemm"]:
-            mask_acc = np.zeros(n_out, np.float32)
+            mask_acc = np.zeros(n_span, np.float32)
             calc.do_batch_gemm(tt.tensor(out_role, mask_acc, dtype=abi.FP32), tt.tensor("xMask", sizes_key="xSizes2"),
                                tt.tensor("wMask", sizes_key="wSizes2"), op)
-            calc.do_memory_write(acc_t, tt.tensor(out_role, mask_acc, dtype=abi.FP32), abi.RED_ADD, 0)
+            calc.do_memory_write(tt.tensor(out_role, acc, dtype=abi.FP32, flat=True), tt.tensor(out_role, mask_acc, dtype=abi.FP32, flat=True), abi.RED_ADD, 0)
         cast = abi.make_cast_params(t["conversionRoundingMode"], relu=t["reluEn"], clip_fp=clip, clip_inf_in=t["clipInfIn"],
                                     flush_denorms=t["flushDenormals"], stochastic_ftz_fp8=t["stochasticFlush"])
-        calc.do_activation(mme_out_t, acc_t, cast)
+        calc.do_activation(tt.tensor(out_role, mme_out, flat=True), tt.tensor(out_role, acc, dtype=abi.FP32, flat=True), cast)
     out_ref = tt.host[out_role].copy()
-    calc.do_memory_write(tt.tensor(out_role, out_ref), mme_out_t, t["reductionOp"], t["reductionRm"], clip)
-    return out_ref, tt
+    calc.do_memory_write(tt.tensor(out_role, out_ref, flat=True), tt.tensor(out_role, mme_out, flat=True), t["reductionOp"], t["reductionRm"], clip)
+    return out_ref
+
+
+def run_test(calc, t, tensors=None):
+    """One test on the backend; returns (output buffer in its dtype and layout, TestTensors)."""
+    tt = tensors or TestTensors(t, calc)
+    return run_flow(calc, t, tt), tt
 
 
 OP_NAMES = {v: k for k, v in OPERATIONS.items()}

@@ -70,6 +70,8 @@ struct mmeb200_ctx {
     cudaEvent_t ev_scatter = nullptr, ev_gather = nullptr;
     bool gather_pending = false;
     uint64_t launches = 0;
+    void* aux = nullptr;            // dense copies of strided convolution tensors (outlives the per-call arena)
+    size_t aux_bytes = 0;
 
     int fail(int code, const char* fmt, ...) {
         char buf[512];
@@ -1051,6 +1053,7 @@ void mmeb200_destroy(mmeb200_ctx* c) {
         cudaEventDestroy(c->ev_gather);
     }
     for (auto& b : c->arena) cudaFree(b.ptr);
+    if (c->aux) cudaFree(c->aux);
     if (c->d_status) cudaFree(c->d_status);
     if (c->h_status) cudaFreeHost(c->h_status);
     if (c->d_jump) cudaFree(c->d_jump);
@@ -1403,11 +1406,66 @@ static int conv_fast_path(mmeb200_ctx* c, const mmeb200_tensor* x, const mmeb200
     return 0;
 }
 
+int mmeb200_dma(mmeb200_ctx* c, mmeb200_tensor* out, const mmeb200_tensor* x, int op);
+
+// Convolution tensors with gaps (element strides beyond the dense ones; the reference builds such tensors for its
+// strided test cases, mme/mme_verification/common/mme_test_data_gen.cpp:222-298): the operands that are read are
+// gathered into dense device copies, the convolution runs on dense tensors, and a strided result is scattered through the
+// output's own strides, which leaves the gaps of a caller-owned buffer as they were (dedx writes in place,
+// mme_reference_impl.cpp:858-861).
+static int conv_with_strided_tensors(mmeb200_ctx* c, mmeb200_tensor* out, const mmeb200_tensor* x, const mmeb200_tensor* w,
+                                     const mmeb200_tensor* y, const mmeb200_conv_params* p, int op, int rounding,
+                                     const mmeb200_cast_params* cast) {
+    const int base_op = op == MMEB200_OP_TRANSPOSED_DEDX ? MMEB200_OP_DEDX : op == MMEB200_OP_DETERMINISTIC_DEDW ? MMEB200_OP_DEDW : op;
+    const mmeb200_tensor* in[3] = {x, w, y};
+    const bool read[3] = {base_op != MMEB200_OP_DEDX, base_op != MMEB200_OP_DEDW, base_op != MMEB200_OP_FWD};
+    size_t need = 0, off[4] = {0, 0, 0, 0};
+    for (int i = 0; i < 3; ++i)
+        if (read[i] && !is_dense(in[i])) { off[i] = need; need += (num_elems(in[i]) * dtype_size(in[i]->dtype) + 255) & ~size_t(255); }
+    if (!is_dense(out)) { off[3] = need; need += (num_elems(out) * dtype_size(out->dtype) + 255) & ~size_t(255); }
+    if (need > c->aux_bytes) {
+        CUDA_OK(c, cudaStreamSynchronize(c->stream));
+        if (c->aux) CUDA_OK(c, cudaFree(c->aux));
+        c->aux = nullptr; c->aux_bytes = 0;
+        CUDA_OK(c, cudaMalloc(&c->aux, need));
+        c->aux_bytes = need;
+    }
+    auto dense_view = [&](const mmeb200_tensor* t, size_t offset) {
+        mmeb200_tensor d = *t;
+        uint32_t acc = 1;
+        for (int k = 0; k < 5; ++k) { d.strides[k] = acc; acc *= d.sizes[k]; }
+        d.data = static_cast<char*>(c->aux) + offset;
+        d.mem_space = MMEB200_MEM_DEVICE;
+        return d;
+    };
+    mmeb200_tensor d[3], d_out;
+    for (int i = 0; i < 3; ++i) {
+        d[i] = *in[i];
+        if (is_dense(in[i])) continue;
+        d[i] = dense_view(in[i], read[i] ? off[i] : 0);   // a tensor that is not read only lends its sizes
+        if (read[i]) TRY(mmeb200_dma(c, &d[i], in[i], MMEB200_OP_MEMCPY));
+    }
+    const bool scatter = !is_dense(out);
+    if (scatter) d_out = dense_view(out, off[3]);
+    TRY(mmeb200_conv(c, scatter ? &d_out : out, &d[0], &d[1], &d[2], p, op, rounding, cast));
+    if (scatter) TRY(mmeb200_dma(c, out, &d_out, MMEB200_OP_MEMCPY));
+    return 0;
+}
+
 int mmeb200_conv(mmeb200_ctx* c, mmeb200_tensor* out, const mmeb200_tensor* x, const mmeb200_tensor* w, const mmeb200_tensor* y,
                  const mmeb200_conv_params* p, int op, int rounding, const mmeb200_cast_params* cast) {
     if (!c) return MMEB200_ERR_INVALID_ARG;
     cudaSetDevice(c->device);
     if (!p) return c->fail(MMEB200_ERR_INVALID_ARG, "null convolution parameters");
+    if (out && x && w && y && out->dims >= 1 && out->dims <= 5 && x->dims >= 1 && x->dims <= 5 && w->dims >= 1 && w->dims <= 5 && y->dims >= 1 &&
+        y->dims <= 5 && num_elems(out) && num_elems(x) && num_elems(w) && num_elems(y) &&
+        (!is_dense(out) || !is_dense(x) || !is_dense(w) || !is_dense(y))) {
+        TRY(check_tensor(c, out, "output"));
+        TRY(check_tensor(c, x, "x"));
+        TRY(check_tensor(c, w, "w"));
+        TRY(check_tensor(c, y, "y"));
+            return conv_with_strided_tensors(c, out, x, w, y, p, op, rounding, cast);
+    }
     if (op == MMEB200_OP_DETERMINISTIC_DEDW) op = MMEB200_OP_DEDW;
     const bool transposed = (op == MMEB200_OP_TRANSPOSED_DEDX);
     if (transposed) op = MMEB200_OP_DEDX;

@@ -39,7 +39,8 @@ enum : uint32_t {
     WAIT_PRODUCER_EMPTY = 1,
     WAIT_MMA_FULL = 2,
     WAIT_MMA_TMEM_EMPTY = 3,
-    WAIT_EPILOGUE_TMEM_FULL = 4
+    WAIT_EPILOGUE_TMEM_FULL = 4,
+    SMEM_MISALIGNED = 5
 };
 
 struct ConvGeom {
@@ -112,9 +113,12 @@ struct GemmSmem {
     static constexpr int kABytes = kBlockM * kRowBytes;
     static constexpr int kBBytes = BLOCK_N * kRowBytes;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kBarrierBytes = 1024;   // keeps the output staging buffers 1024-byte aligned
+    static constexpr int kBarrierBytes = 256;    // after the staging buffers, which need 1024-byte alignment
     static constexpr int kOutStageBytes = 2 * kBlockM * kRowBytes;
-    static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + kOutStageBytes + 1024 /* alignment slack */;
+    // No alignment slack: the dynamic shared memory is declared 1024-byte aligned and the kernel checks it. The CTA then
+    // leaves about 2.8 KB of the SM's shared memory free, enough for a small block of another kernel (the dedw exchange's
+    // wait-and-add kernels) to share the SM with it.
+    static constexpr int kTotal = STAGES * kStageBytes + kOutStageBytes + kBarrierBytes;
 };
 
 struct TileCoord {
@@ -160,18 +164,19 @@ __device__ __forceinline__ void epilogue_random4(const GemmParams& p, uint64_t f
 // measured slower for stochastic rounding into bf16, 0.55 against 0.46 ms on 8192^3, and the same for fp8).
 constexpr int kEpiFlatUnroll = 8;
 
-// bf16 output in any rounding mode, straight-line: 32 values in v become 16 packed words.
+// bf16 output in any rounding mode, straight-line: 32 values in v become 16 packed words. Stochastic rounding draws one
+// Philox block per EIGHT elements (16 random bits each, philox_halves8); the stream position of the 32 is a multiple of 8.
 template <int RM>
 __device__ __forceinline__ void epilogue_bf16_flat(uint32_t (&v)[32], const GemmParams& p, uint64_t flat_index) {
     const bool clip = p.cast.clip, ftz = p.cast.ftz, clip_inf_in = p.cast.clip_inf_in;
-#pragma unroll kEpiFlatUnroll
-    for (int q = 0; q < 8; ++q) {
-        uint32_t rnd[4], o[4];
-        epilogue_random4<RM == RM_SR>(p, flat_index, q, rnd);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) o[e] = f32_to_bf16_flat<RM>(epilogue_prepare(v[4 * q + e], p), rnd[e], clip, ftz, clip_inf_in);
-        v[2 * q] = o[0] | (o[1] << 16);       // words 2q, 2q+1 lie below every value still to be read
-        v[2 * q + 1] = o[2] | (o[3] << 16);
+    for (int g = 0; g < 4; ++g) {
+        uint32_t rnd[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u}, o[8];
+        if (RM == RM_SR && p.rng_philox) philox_halves8(p.rng_seed, p.rng_offset, flat_index + 8 * g, rnd);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = f32_to_bf16_flat<RM>(epilogue_prepare(v[8 * g + e], p), rnd[e], clip, ftz, clip_inf_in);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[4 * g + e] = o[2 * e] | (o[2 * e + 1] << 16);   // words 4g .. 4g+3 lie below every value still to be read
     }
 }
 
@@ -193,7 +198,7 @@ __device__ __forceinline__ void epilogue_fp8_flat(uint32_t (&v)[32], const GemmP
 // The general cast, every flag and every input: a few hundred instructions per element with data-dependent branches.
 // It runs as a rolled loop over groups of four elements of an array that the loop may index, which keeps the code small.
 __device__ __forceinline__ void epilogue_general(uint32_t (&t)[32], const GemmParams& p, uint32_t out_elem, uint64_t flat_index) {
-    const bool philox = p.rng_philox != 0, aligned = ((p.rng_offset + flat_index) & 3u) == 0;
+    const bool philox = p.rng_philox != 0, aligned = ((p.rng_offset + flat_index) & 3u) == 0 && p.cast.out_dtype != DT_BF16;
 #pragma unroll 1
     for (int q = 0; q < 8; ++q) {
         uint32_t rnd[4] = {0u, 0u, 0u, 0u};
@@ -202,7 +207,7 @@ __device__ __forceinline__ void epilogue_general(uint32_t (&t)[32], const GemmPa
                 philox_words4(p.rng_seed, p.rng_offset, flat_index + 4 * q, rnd);
             } else {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) rnd[e] = philox_word(p.rng_seed, p.rng_offset, flat_index + 4 * q + e);
+                for (int e = 0; e < 4; ++e) rnd[e] = cast_random_word(int(p.cast.out_dtype), p.rng_seed, p.rng_offset, flat_index + 4 * q + e);
             }
         }
 #pragma unroll
@@ -270,7 +275,7 @@ __device__ __forceinline__ void epilogue_convert(uint32_t (&v)[32], const GemmPa
         }
     } else {
         // bf16 in the other rounding modes: some twenty instructions per element, inlined on the accumulator registers
-        if (p.cast.out_dtype == DT_BF16 && (!p.rng_philox || ((p.rng_offset + flat_index) & 3u) == 0)) {
+        if (p.cast.out_dtype == DT_BF16 && (!p.rng_philox || ((p.rng_offset + flat_index) & 7u) == 0)) {
             switch (p.cast.rm) {
                 case RM_NE: epilogue_bf16_flat<RM_NE>(v, p, flat_index); break;
                 case RM_UP: epilogue_bf16_flat<RM_UP>(v, p, flat_index); break;
@@ -608,9 +613,13 @@ template <int KIND, int BLOCK_N, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     using S = GemmSmem<BLOCK_N, STAGES>;
     if (launch_is_predicated_off(p.pred, p.pred_nonzero)) return;   // uniform over the grid, before anything is set up
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * S::kStageBytes);
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw;
+    if (smem_u32(smem) & 1023u) {   // the operand stages and the staging buffers need 1024-byte alignment (128-byte swizzle)
+        if (threadIdx.x == 0) atomicCAS(p.status, 0u, SMEM_MISALIGNED);
+        return;
+    }
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * S::kStageBytes + S::kOutStageBytes);
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* tmem_full_bar = empty_bar + STAGES;
     uint64_t* tmem_empty_bar = tmem_full_bar + 2;
@@ -747,7 +756,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
         const uint32_t sub = warp & 3;  // tensor-memory sub-partition this warp may read
         uint32_t acc = 0, acc_phase = 0;
         const uint32_t out_elem = dtype_size(int(p.out_dtype));
-        uint8_t* stage_out = smem + STAGES * S::kStageBytes + S::kBarrierBytes;  // 2 x [128 rows x 128 B], 1024-aligned
+        uint8_t* stage_out = smem + STAGES * S::kStageBytes;  // 2 x [128 rows x 128 B], 1024-aligned
         uint32_t store_buf = 0;
         for (uint32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
             const TileCoord tc = decode_tile(p, t);

@@ -33,9 +33,9 @@ struct PairSmem {
     static constexpr int kABytes = kBlockM * kRowBytes;
     static constexpr int kBBytes = (kPairBlockN / 2) * kRowBytes;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kBarrierBytes = 1024;
+    static constexpr int kBarrierBytes = 256;
     static constexpr int kOutStageBytes = EPI_GROUPS * 2 * kBlockM * kRowBytes;
-    static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + kOutStageBytes + 1024;
+    static constexpr int kTotal = kStages * kStageBytes + kOutStageBytes + kBarrierBytes;   // see GemmSmem::kTotal
     static constexpr int kThreads = 128 + 128 * EPI_GROUPS;
 };
 
@@ -49,9 +49,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<EPI_GROUPS>
     using S = PairSmem<EPI_GROUPS>;
     constexpr int STAGES = S::kStages;
     if (launch_is_predicated_off(p.pred, p.pred_nonzero)) return;   // uniform over the grid (both CTAs of every pair)
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * S::kStageBytes);
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw;
+    if (smem_u32(smem) & 1023u) {   // uniform over the cluster: both CTAs see the same offset
+        if (threadIdx.x == 0) atomicCAS(p.status, 0u, SMEM_MISALIGNED);
+        return;
+    }
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * S::kStageBytes + S::kOutStageBytes);
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* tmem_full_bar = empty_bar + STAGES;
     uint64_t* tmem_empty_bar = tmem_full_bar + 2;
@@ -175,7 +179,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<EPI_GROUPS>
         constexpr int kGroupCols = kPairBlockN / EPI_GROUPS;
         uint32_t acc = 0, acc_phase = 0;
         const uint32_t out_elem = dtype_size(int(p.out_dtype));
-        uint8_t* stage_out = smem + STAGES * S::kStageBytes + S::kBarrierBytes + grp * (2 * kBlockM * kRowBytes);
+        uint8_t* stage_out = smem + STAGES * S::kStageBytes + grp * (2 * kBlockM * kRowBytes);
         uint32_t store_buf = 0;
         const uint32_t leader_tmem_empty = mapa_shared(smem_u32(&tmem_empty_bar[0]), 0);
         for (uint32_t t = pair; t < total_tiles; t += num_pairs) {

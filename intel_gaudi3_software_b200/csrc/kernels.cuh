@@ -99,10 +99,11 @@ __global__ void cast_kernel(void* __restrict__ out, uint32_t* __restrict__ acc, 
                 if (changed) reinterpret_cast<uint4*>(acc)[q] = make_uint4(b[g][0], b[g][1], b[g][2], b[g][3]);
             }
             uint32_t rnd[4] = {0u, 0u, 0u, 0u};
-            if (block_rng) philox_words4(seed, offset, q * 4, rnd);
+            if (block_rng && c.out_dtype == DT_BF16) philox_halves4(seed, offset, q * 4, rnd);
+            else if (block_rng) philox_words4(seed, offset, q * 4, rnd);
             else if (rng_philox) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) rnd[j] = philox_word(seed, offset, q * 4 + j);
+                for (int j = 0; j < 4; ++j) rnd[j] = cast_random_word(c.out_dtype, seed, offset, q * 4 + j);
             }
             uint32_t w[4];
             cast_group4(b[g], rnd, c, tier, w);
@@ -119,7 +120,7 @@ __global__ void cast_kernel(void* __restrict__ out, uint32_t* __restrict__ acc, 
             if (r != bits) acc[i] = r;
             bits = r;
         }
-        const uint32_t rnd = rng_philox ? philox_word(seed, offset, i) : 0u;
+        const uint32_t rnd = rng_philox ? cast_random_word(c.out_dtype, seed, offset, i) : 0u;
         store_cast(out, i, cast_from_f32(bits, c, rnd), elem);
     }
 }
@@ -376,7 +377,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, ReduceOut r) 
         if (f32_is_nan(bits)) bits = kF32CanonNan;
         if (r.has_cast) {
             if (r.cast.relu) bits = relu_bits(bits);
-            bits = cast_from_f32(bits, r.cast, r.rng_philox ? philox_word(r.seed, r.offset, i) : 0u);
+            bits = cast_from_f32(bits, r.cast, r.rng_philox ? cast_random_word(r.cast.out_dtype, r.seed, r.offset, i) : 0u);
         }
         uint64_t b = i / per;
         const uint64_t rem = i % per;
@@ -411,7 +412,7 @@ __global__ void splitk_reduce_vec4_kernel(const float* __restrict__ ws, ReduceOu
             if (f32_is_nan(bits[j])) bits[j] = kF32CanonNan;
             if (r.has_cast) {
                 if (r.cast.relu) bits[j] = relu_bits(bits[j]);
-                bits[j] = cast_from_f32(bits[j], r.cast, r.rng_philox ? philox_word(r.seed, r.offset, i + j) : 0u);
+                bits[j] = cast_from_f32(bits[j], r.cast, r.rng_philox ? cast_random_word(r.cast.out_dtype, r.seed, r.offset, i + j) : 0u);
             }
         }
         uint64_t b = i / per;

@@ -615,6 +615,43 @@ MME_HD void philox_words4(uint64_t seed, uint64_t offset, uint64_t index4, uint3
     philox4x32_10(c, uint32_t(seed), uint32_t(seed >> 32));
     for (int j = 0; j < 4; ++j) w[j] = c[j] ? c[j] : 1u;
 }
+// 16-bit output types (bf16) discard 16 bits, so 16 random bits decide an element exactly: the element at stream
+// position pos takes half (pos & 1) of word ((pos >> 1) & 3) of block (pos >> 3) -- one Philox block serves EIGHT elements --
+// as the word (h << 16) | 0x8000. Rounding up when (discarded << 16) >= word then happens with probability
+// discarded / 2^16 exactly, and never for an exactly representable value. The third counter word is 1, which keeps this
+// stream apart from the 32-bit one above.
+MME_HD uint32_t philox_half(uint64_t seed, uint64_t offset, uint64_t index) {
+    const uint64_t pos = offset + index, ctr = pos >> 3;
+    uint32_t c[4] = {uint32_t(ctr), uint32_t(ctr >> 32), 1u, 0u};
+    philox4x32_10(c, uint32_t(seed), uint32_t(seed >> 32));
+    const uint32_t w = c[(pos >> 1) & 3u];
+    return ((((pos & 1u) ? (w >> 16) : w) & 0xFFFFu) << 16) | 0x8000u;
+}
+// the eight words of elements index8 .. index8 + 7 (offset + index8 a multiple of 8)
+MME_HD void philox_halves8(uint64_t seed, uint64_t offset, uint64_t index8, uint32_t (&w)[8]) {
+    const uint64_t ctr = (offset + index8) >> 3;
+    uint32_t c[4] = {uint32_t(ctr), uint32_t(ctr >> 32), 1u, 0u};
+    philox4x32_10(c, uint32_t(seed), uint32_t(seed >> 32));
+    for (int j = 0; j < 4; ++j) {
+        w[2 * j] = (c[j] << 16) | 0x8000u;
+        w[2 * j + 1] = (c[j] & 0xFFFF0000u) | 0x8000u;
+    }
+}
+// the four words of elements index4 .. index4 + 3 (offset + index4 a multiple of 4): half a block
+MME_HD void philox_halves4(uint64_t seed, uint64_t offset, uint64_t index4, uint32_t (&w)[4]) {
+    const uint64_t pos = offset + index4, ctr = pos >> 3;
+    uint32_t c[4] = {uint32_t(ctr), uint32_t(ctr >> 32), 1u, 0u};
+    philox4x32_10(c, uint32_t(seed), uint32_t(seed >> 32));
+    const int first = (pos & 4u) ? 2 : 0;
+    for (int j = 0; j < 2; ++j) {
+        w[2 * j] = (c[first + j] << 16) | 0x8000u;
+        w[2 * j + 1] = (c[first + j] & 0xFFFF0000u) | 0x8000u;
+    }
+}
+// The random word of one element of a cast: which of the two streams applies follows from the output type.
+MME_HD uint32_t cast_random_word(int out_dtype, uint64_t seed, uint64_t offset, uint64_t index) {
+    return out_dtype == DT_BF16 ? philox_half(seed, offset, index) : philox_word(seed, offset, index);
+}
 
 // ---------------------------------------------------------------------------------------------
 // Element comparison of the reference's TensorComparator

@@ -118,6 +118,16 @@ uint32_t hc_g3_dot_tf32(const uint32_t* a, const uint32_t* b, size_t n)
 int hc_fp8_foreign(uint32_t code, int exp_width, int mode) { return fp8_code_is_foreign(code, exp_width, mode); }
 uint32_t hc_lfsr(uint32_t v, uint32_t poly) { return lfsr32_step(v, poly); }
 uint32_t hc_philox(uint64_t seed, uint64_t offset, uint64_t index) { return philox_word(seed, offset, index); }
+uint32_t hc_philox_half(uint64_t seed, uint64_t offset, uint64_t index) { return philox_half(seed, offset, index); }
+void hc_philox_halves(uint64_t seed, uint64_t offset, uint64_t index8, uint32_t* w8, uint32_t* w4a, uint32_t* w4b)
+{
+    uint32_t a[8], b[4], c[4];
+    philox_halves8(seed, offset, index8, a);
+    philox_halves4(seed, offset, index8, b);
+    philox_halves4(seed, offset, index8 + 4, c);
+    for (int i = 0; i < 8; i++) w8[i] = a[i];
+    for (int i = 0; i < 4; i++) { w4a[i] = b[i]; w4b[i] = c[i]; }
+}
 void hc_philox_block(uint32_t* c, uint32_t k0, uint32_t k1)
 {
     uint32_t s[4] = {c[0], c[1], c[2], c[3]};

@@ -5,6 +5,7 @@ import glob
 import json
 import os
 
+import numpy as np
 import pytest
 
 from intel_gaudi3_software_b200 import abi
@@ -106,3 +107,34 @@ def test_reference_corpus_parses():
             except cr.ConfigError:
                 rejected += 1
     assert parsed > 500 and parsed > 3 * rejected, (parsed, rejected)
+
+
+def test_corpus_fixture_lists_the_named_files():
+    """tests/golden/reference_corpus_cases.json (the GPU corpus test's input) holds the expansion of these files of the reference."""
+    import json
+    with open(os.path.join(os.path.dirname(__file__), "golden", "reference_corpus_cases.json")) as f:
+        doc = json.load(f)
+    names = {os.path.splitext(os.path.basename(rel))[0]: len(e["tests"]) for rel, e in doc["files"].items()}
+    assert names == {"basic_fwd": 14, "basic_dedx": 12, "basic_dedw": 12, "basic_ab": 1, "basic_abt": 1, "basic_atb": 1, "basic_atbt": 1,
+                     "basic_ab_strides": 1, "basic_fwd_strides": 1, "basic_dual_gemm": 14, "numerics_fp8": 216, "stochastic_rounding": 2}
+
+
+def test_dual_gemm_becomes_two_tests_and_strided_tensors_keep_their_gaps():
+    doc = {"tests": [[{"testName": ["dual"]}, {"inTypeFloat": ["bf16"]}, {"outTypeFloat": ["fp32"]}, {"operation": ["ab"]}, {"dualGemm": ["true"]},
+                      {"xSizes": ["12", "7"]}, {"wSizes": ["5", "12"]}, {"ySizes": ["5", "7"]},
+                      {"xSizes2": ["9", "4"]}, {"wSizes2": ["3", "9"]}, {"ySizes2": ["3", "4"]},
+                      {"xStrides": ["1", "16", "200", "200", "200"]}]]}
+    first, second = cr.Parser(3).parse(doc)
+    assert first["xSizes"][:2] == [12, 7] and second["xSizes"][:2] == [9, 4] and second["ySizes"][:2] == [3, 4]
+    assert not first["dualGemm"] and not second["dualGemm"] and first["seed"] != second["seed"]
+
+    class FillOnes:   # stands in for the device generator: every generated value is 1.0 (bf16 0x3F80)
+        def generate(self, tensor, kind, lo=0.0, hi=0.0, mean=0.0, std=0.0, seed=0, packing=0, level=0):
+            n = int(np.prod(list(tensor.sizes)))
+            np.frombuffer((cr.abi.C.c_uint16 * n).from_address(tensor.data), dtype=np.uint16)[:] = 0x3F80
+    tt = cr.TestTensors(first, FillOnes())
+    assert tt.strides("x") == [1, 16, 200, 200, 200] and tt.span("x") == 1 + 11 + 6 * 16 and tt.strides("w") is None
+    buf = tt.host["x"]
+    assert buf.size == tt.span("x") and (tt.logical("x", buf) == 0x3F80).all() and int((buf == 0x3F80).sum()) == 12 * 7
+    desc = tt.tensor("x")
+    assert list(desc.strides)[:2] == [1, 16] and list(desc.sizes)[:2] == [12, 7]

@@ -162,6 +162,26 @@ def test_philox_known_answers(hc):
     assert block([0x243F6A88, 0x85A308D3, 0x13198A2E, 0x03707344], [0xA4093822, 0x299F31D0]) == [0xD16CFE09, 0x94FDCCEB, 0x5001E420, 0x24126EA1]
 
 
+def test_philox_half_stream_for_16_bit_outputs(hc):
+    """bf16 casts draw 16 random bits per element, eight elements per Philox block: the per-element, per-four and per-eight
+    forms agree, the words are (h << 16) | 0x8000 with h uniform, and a different stream from the 32-bit one."""
+    hc.hc_philox_half.restype = C.c_uint32
+    hc.hc_philox.restype = C.c_uint32
+    w8, w4a, w4b = (np.zeros(8, np.uint32), np.zeros(4, np.uint32), np.zeros(4, np.uint32))
+    for base in (0, 8, 4096):
+        hc.hc_philox_halves(C.c_uint64(9), C.c_uint64(16), C.c_uint64(base), w8.ctypes.data_as(C.c_void_p), w4a.ctypes.data_as(C.c_void_p),
+                            w4b.ctypes.data_as(C.c_void_p))
+        single = np.array([hc.hc_philox_half(C.c_uint64(9), C.c_uint64(16), C.c_uint64(base + i)) for i in range(8)], dtype=np.uint32)
+        assert (w8 == single).all() and (np.concatenate([w4a, w4b]) == single).all()
+        assert (hc.hc_philox_half(C.c_uint64(9), C.c_uint64(0), C.c_uint64(base + 16)) == single[0])   # offset and index add up
+    w = np.array([hc.hc_philox_half(C.c_uint64(5), C.c_uint64(0), C.c_uint64(i)) for i in range(40000)], dtype=np.uint64)
+    assert ((w & 0xFFFF) == 0x8000).all()
+    h = (w >> 16).astype(np.float64)
+    assert abs(h.mean() / 65536 - 0.5) < 0.01 and len(np.unique(h)) > 15000
+    w32 = np.array([hc.hc_philox(C.c_uint64(5), C.c_uint64(0), C.c_uint64(i)) for i in range(64)], dtype=np.uint64)
+    assert ((w32 >> 16) != (w[:64] >> 16)).mean() > 0.9
+
+
 def test_philox_word_never_zero_and_uniform(hc):
     hc.hc_philox.restype = C.c_uint32
     w = np.array([hc.hc_philox(C.c_uint64(5), C.c_uint64(0), C.c_uint64(i)) for i in range(20000)], dtype=np.uint64)

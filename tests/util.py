@@ -113,3 +113,24 @@ def assert_acc(gpu, ref, sabs, name=""):
     err = acc_error(np.asarray(gpu).reshape(-1), np.asarray(ref).reshape(-1), np.asarray(sabs, dtype=np.float64).reshape(-1))
     assert err <= ACC_TOL, "%s: accumulator error %.3g * sum|ab| exceeds %.0e" % (name, err, ACC_TOL)
     return err
+
+
+class OracleAsCalculator:
+    """A CPU checker behind the calculator's method names, so that the config runner's flow (run_flow) can replay a test on
+    it. Raises where the backend would."""
+
+    def __init__(self, oracle, lfsr, poly, chip=abi.CHIP_GAUDI3):
+        self.oracle, self.lfsr, self.poly, self.chip = oracle, lfsr, poly, chip
+
+    def do_convolution(self, out, x, w, y, params, op, rm=abi.RM_NE, cast=None):
+        assert cast is None and self.oracle.conv(out, x, w, y, params, op, rm, chip=self.chip) == 0
+
+    def do_batch_gemm(self, out, x, w, op, cast=None):
+        assert cast is None and self.oracle.bgemm(out, x, w, op, chip=self.chip) == 0
+
+    def do_memory_write(self, mem, mme_out, reduction_op=abi.RED_NONE, reduction_rm=0, clip_fp=False):
+        assert self.oracle.memory_write(mem, mme_out, reduction_op, reduction_rm, clip_fp, chip=self.chip) == 0
+
+    def do_activation(self, out, acc, cast):
+        rc, self.lfsr = self.oracle.activation(out, acc, cast, self.lfsr, self.poly, chip=self.chip)
+        assert rc == 0
