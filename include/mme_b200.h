@@ -106,11 +106,10 @@ enum {
     MMEB200_RNG_LFSR = 0,   /* the reference's per-lane Galois LFSRs: bit-exact, standalone cast only */
     MMEB200_RNG_PHILOX = 1  /* counter-based Philox4x32-10 keyed by (seed, element position), the same stream whether the
                                cast is fused into a GEMM / convolution or runs alone. Position pos = rng_offset + flat
-                               element index. fp8 (and flagged fp32) outputs: 32 random bits per element, word (pos & 3) of
-                               block (pos >> 2), a zero word replaced by 1. bf16 outputs discard 16 bits, so they draw 16:
-                               half (pos & 1) of word ((pos >> 1) & 3) of block (pos >> 3), third counter word 1, used as
-                               (h << 16) | 0x8000 -- one block serves eight elements and P(round up) is exactly the
-                               discarded fraction */
+                               element index; the element draws 16 random bits: half (pos & 1) of word ((pos >> 1) & 3)
+                               of block (pos >> 3) (third counter word 1), used as (h << 16) | 0x8000 against the
+                               left-aligned discarded bits. One block serves eight elements. bf16: P(round up) is exactly
+                               the discarded fraction; fp8: that fraction rounded to 16 bits */
 };
 
 /* Tensor descriptor: the plain-data image of MmeSimTensor (sim_tensor.h:9-52,

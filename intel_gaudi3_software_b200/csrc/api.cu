@@ -587,12 +587,65 @@ static int repack(mmeb200_ctx* c, const LogicalOperand& in, PrepKind kind, TmaOp
     const uint64_t block_k = kRowBytes / dst_elem;
     const uint64_t seg = (segs == 1) ? in.k : ((in.k + block_k - 1) / block_k) * block_k;
     const uint64_t align = 16 / dst_elem;
-    const uint64_t ld = ((seg * segs + align - 1) / align) * align;
     const uint64_t batches = uint64_t(in.bsz[0]) * in.bsz[1] * in.bsz[2];
+    // Operands with a contiguous dimension keep their orientation and are converted four elements at a time
+    // (repack_vec4_kernel); anything else is gathered element by element into a K-major copy.
+    {
+        const bool k_contig = in.k_stride == 1, mn_contig = in.mn_stride == 1 && !k_contig;
+        const uint64_t C_ = k_contig ? in.k : in.mn, R_ = k_contig ? in.mn : in.k, rs = k_contig ? in.mn_stride : in.k_stride;
+        bool ok = (k_contig || mn_contig) && C_ % 4 == 0 && rs % 4 == 0 && (reinterpret_cast<uintptr_t>(in.ptr) % (4 * src_elem)) == 0 && R_ && C_;
+        if (mn_contig && src_elem == 4) ok = false;   // 32-bit operands must reach the tensor cores K-major: transposed below
+        for (int i = 0; i < 3; ++i) ok = ok && (in.bsz[i] == 1 || in.bstride[i] % 4 == 0);
+        if (ok) {
+            RepackVecParams v;
+            memset(&v, 0, sizeof v);
+            v.pred = pred; v.pred_nonzero = pred_nonzero;
+            const uint64_t c_ext = k_contig ? seg * segs : C_;
+            const uint64_t ld = ((c_ext + align - 1) / align) * align;
+            const uint64_t rows_out = k_contig ? R_ : seg * segs;
+            void* dst = nullptr;
+            const size_t bytes = size_t(batches) * rows_out * ld * dst_elem;
+            TRY(arena_alloc(c, &dst, bytes));
+            if (seg != in.k || ld != c_ext) CUDA_OK(c, cudaMemsetAsync(dst, 0, bytes, c->stream));   // padding reads as zeros
+            v.src = in.ptr; v.dst = dst; v.R = R_; v.C = C_; v.r_stride = rs;
+            for (int i = 0; i < 3; ++i) { v.bstride[i] = in.bstride[i]; v.bsz[i] = in.bsz[i]; }
+            v.dst_ld = ld; v.dst_batch = rows_out * ld; v.seg = seg; v.seg_along_c = k_contig ? 1 : 0;
+            v.mode = r.mode; v.src_elem = src_elem; v.dtype = in.dtype; v.bias = in.bias; v.inf_nan = in.mode;
+            repack_vec4_kernel<<<grid_for(batches * R_ * (C_ / 4), 256, c->sm_count), 256, 0, c->stream>>>(v);
+            c->launches++;
+            CUDA_OK(c, cudaGetLastError());
+            out->ptr = dst; out->elem = dst_elem; out->mn_major = !k_contig;
+            out->inner = k_contig ? seg * segs : in.mn;
+            out->rows = rows_out; out->row_stride = ld;
+            uint64_t bs = v.dst_batch;
+            for (int i = 0; i < 3; ++i) { out->bsz[i] = in.bsz[i]; out->bstride[i] = bs; bs *= in.bsz[i]; }
+            *k_out = seg * segs;
+            return 0;
+        }
+    }
+    const uint64_t ld = ((seg * segs + align - 1) / align) * align;
     void* dst = nullptr;
     const size_t bytes = size_t(batches) * in.mn * ld * dst_elem;
     TRY(arena_alloc(c, &dst, bytes));
     if (segs > 1 || ld != in.k) CUDA_OK(c, cudaMemsetAsync(dst, 0, bytes, c->stream));
+    if (src_elem == 4 && r.mode >= 2 && in.mn_stride == 1 && in.k_stride != 1 && in.mn && in.k) {
+        // fp32 / tf32 with M or N contiguous: tiled transpose into the K-major copy (repack_transpose_f32_kernel)
+        RepackTransposeParams t;
+        memset(&t, 0, sizeof t);
+        t.src = static_cast<const uint32_t*>(in.ptr); t.dst = static_cast<uint32_t*>(dst);
+        t.mn = in.mn; t.k = in.k; t.k_stride = in.k_stride;
+        for (int i = 0; i < 3; ++i) { t.bstride[i] = in.bstride[i]; t.bsz[i] = in.bsz[i]; }
+        t.dst_ld = ld; t.seg = seg; t.mode = r.mode;
+        const uint64_t tiles = ((in.mn + 31) / 32) * ((in.k + 31) / 32) * batches;
+        repack_transpose_f32_kernel<<<unsigned(std::min<uint64_t>(tiles, uint64_t(c->sm_count) * 32)), 256, 0, c->stream>>>(t);
+        c->launches++;
+        CUDA_OK(c, cudaGetLastError());
+        out->ptr = dst; out->elem = dst_elem; out->mn_major = false; out->inner = seg * segs; out->rows = in.mn; out->row_stride = ld;
+        uint64_t bs2 = in.mn * ld;
+        for (int i = 0; i < 3; ++i) { out->bsz[i] = in.bsz[i]; out->bstride[i] = bs2; bs2 *= in.bsz[i]; }
+        *k_out = seg * segs;
+        return 0;
+    }
     r.src = in.ptr; r.dst = dst; r.rows = in.mn; r.k = in.k; r.row_stride = in.mn_stride; r.k_stride = in.k_stride;
     for (int i = 0; i < 3; ++i) { r.bstride[i] = in.bstride[i]; r.bsz[i] = in.bsz[i]; }
     r.dst_ld = ld; r.seg = seg; r.src_elem = src_elem; r.dtype = in.dtype; r.bias = in.bias; r.inf_nan = in.mode;

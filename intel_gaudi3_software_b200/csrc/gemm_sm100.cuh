@@ -153,17 +153,6 @@ __device__ __forceinline__ uint32_t epilogue_prepare(uint32_t acc, const GemmPar
     return bits;
 }
 
-// The random words of elements 4q .. 4q+3 of the 32 (one Philox block; the stream position of the 32 is a multiple of 4).
-template <bool NEEDS_RANDOM>
-__device__ __forceinline__ void epilogue_random4(const GemmParams& p, uint64_t flat_index, int q, uint32_t (&rnd)[4]) {
-    rnd[0] = rnd[1] = rnd[2] = rnd[3] = 0u;
-    if (NEEDS_RANDOM && p.rng_philox) philox_words4(p.rng_seed, p.rng_offset, flat_index + 4 * q, rnd);
-}
-
-// Groups of four elements unrolled in the straight-line casts: all eight (rolling the loop to one group per iteration
-// measured slower for stochastic rounding into bf16, 0.55 against 0.46 ms on 8192^3, and the same for fp8).
-constexpr int kEpiFlatUnroll = 8;
-
 // bf16 output in any rounding mode, straight-line: 32 values in v become 16 packed words. Stochastic rounding draws one
 // Philox block per EIGHT elements (16 random bits each, philox_halves8); the stream position of the 32 is a multiple of 8.
 template <int RM>
@@ -180,34 +169,36 @@ __device__ __forceinline__ void epilogue_bf16_flat(uint32_t (&v)[32], const Gemm
     }
 }
 
-// fp8 output without the flush flags, straight-line: 32 values in v become 8 packed words.
+// fp8 output without the flush flags, straight-line: 32 values in v become 8 packed words. The stochastic modes draw one
+// Philox block per eight elements, as the bf16 cast does.
 template <int RM>
 __device__ __forceinline__ void epilogue_fp8_flat(uint32_t (&v)[32], const GemmParams& p, uint64_t flat_index) {
     const int exp_width = p.cast.exp_width, bias = p.cast.bias, mode = p.cast.mode;
     const bool clip = p.cast.clip, clip_inf_in = p.cast.clip_inf_in;
-#pragma unroll kEpiFlatUnroll
-    for (int q = 0; q < 8; ++q) {
-        uint32_t rnd[4], o[4];
-        epilogue_random4<RM == RM_SR || RM == RM_SR_NE_DNORM>(p, flat_index, q, rnd);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) o[e] = f32_to_fp8_flat<RM>(epilogue_prepare(v[4 * q + e], p), exp_width, bias, rnd[e], mode, clip, clip_inf_in);
-        v[q] = o[0] | (o[1] << 8) | (o[2] << 16) | (o[3] << 24);   // word q lies below every value still to be read
+    for (int g = 0; g < 4; ++g) {
+        uint32_t rnd[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u}, o[8];
+        if ((RM == RM_SR || RM == RM_SR_NE_DNORM) && p.rng_philox) philox_halves8(p.rng_seed, p.rng_offset, flat_index + 8 * g, rnd);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = f32_to_fp8_flat<RM>(epilogue_prepare(v[8 * g + e], p), exp_width, bias, rnd[e], mode, clip, clip_inf_in);
+        v[2 * g] = o[0] | (o[1] << 8) | (o[2] << 16) | (o[3] << 24);        // words 2g, 2g+1 lie below every value still to be read
+        v[2 * g + 1] = o[4] | (o[5] << 8) | (o[6] << 16) | (o[7] << 24);
     }
 }
 
 // The general cast, every flag and every input: a few hundred instructions per element with data-dependent branches.
 // It runs as a rolled loop over groups of four elements of an array that the loop may index, which keeps the code small.
 __device__ __forceinline__ void epilogue_general(uint32_t (&t)[32], const GemmParams& p, uint32_t out_elem, uint64_t flat_index) {
-    const bool philox = p.rng_philox != 0, aligned = ((p.rng_offset + flat_index) & 3u) == 0 && p.cast.out_dtype != DT_BF16;
+    const bool philox = p.rng_philox != 0, aligned = ((p.rng_offset + flat_index) & 3u) == 0;
 #pragma unroll 1
     for (int q = 0; q < 8; ++q) {
         uint32_t rnd[4] = {0u, 0u, 0u, 0u};
         if (philox) {
             if (aligned) {
-                philox_words4(p.rng_seed, p.rng_offset, flat_index + 4 * q, rnd);
+                philox_halves4(p.rng_seed, p.rng_offset, flat_index + 4 * q, rnd);
             } else {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) rnd[e] = cast_random_word(int(p.cast.out_dtype), p.rng_seed, p.rng_offset, flat_index + 4 * q + e);
+                for (int e = 0; e < 4; ++e) rnd[e] = cast_random_word(p.rng_seed, p.rng_offset, flat_index + 4 * q + e);
             }
         }
 #pragma unroll
@@ -228,7 +219,7 @@ __device__ __forceinline__ void epilogue_general(uint32_t (&t)[32], const GemmPa
 // both store paths; its argument lives in local memory, so the caller hands it a copy of the accumulator registers
 // (an array whose address is taken is in memory everywhere, the fast paths included).
 static __device__ __noinline__ void epilogue_cast_any(uint32_t (&v)[32], const GemmParams& p, uint32_t out_elem, uint64_t flat_index) {
-    const bool stream_ok = !p.rng_philox || ((p.rng_offset + flat_index) & 3u) == 0;
+    const bool stream_ok = !p.rng_philox || ((p.rng_offset + flat_index) & 7u) == 0;
     if (stream_ok && dtype_is_fp8(p.cast.out_dtype) && !p.cast.ftz && !p.cast.sftz) {
         switch (p.cast.rm) {
             case RM_UP: epilogue_fp8_flat<RM_UP>(v, p, flat_index); return;
@@ -288,7 +279,7 @@ __device__ __forceinline__ void epilogue_convert(uint32_t (&v)[32], const GemmPa
         }
         // fp8 in the common rounding modes, inlined as well (out of line, through local memory, stochastic rounding
         // measured 0.67 ms on 8192^3 against 0.40 ms inlined); the rarer modes stay out of line to bound the build time
-        if (dtype_is_fp8(p.cast.out_dtype) && !p.cast.ftz && !p.cast.sftz && (!p.rng_philox || ((p.rng_offset + flat_index) & 3u) == 0)) {
+        if (dtype_is_fp8(p.cast.out_dtype) && !p.cast.ftz && !p.cast.sftz && (!p.rng_philox || ((p.rng_offset + flat_index) & 7u) == 0)) {
             switch (p.cast.rm) {
                 case RM_NE: epilogue_fp8_flat<RM_NE>(v, p, flat_index); return;
                 case RM_Z: epilogue_fp8_flat<RM_Z>(v, p, flat_index); return;

@@ -99,11 +99,10 @@ __global__ void cast_kernel(void* __restrict__ out, uint32_t* __restrict__ acc, 
                 if (changed) reinterpret_cast<uint4*>(acc)[q] = make_uint4(b[g][0], b[g][1], b[g][2], b[g][3]);
             }
             uint32_t rnd[4] = {0u, 0u, 0u, 0u};
-            if (block_rng && c.out_dtype == DT_BF16) philox_halves4(seed, offset, q * 4, rnd);
-            else if (block_rng) philox_words4(seed, offset, q * 4, rnd);
+            if (block_rng) philox_halves4(seed, offset, q * 4, rnd);
             else if (rng_philox) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) rnd[j] = cast_random_word(c.out_dtype, seed, offset, q * 4 + j);
+                for (int j = 0; j < 4; ++j) rnd[j] = cast_random_word(seed, offset, q * 4 + j);
             }
             uint32_t w[4];
             cast_group4(b[g], rnd, c, tier, w);
@@ -120,7 +119,7 @@ __global__ void cast_kernel(void* __restrict__ out, uint32_t* __restrict__ acc, 
             if (r != bits) acc[i] = r;
             bits = r;
         }
-        const uint32_t rnd = rng_philox ? cast_random_word(c.out_dtype, seed, offset, i) : 0u;
+        const uint32_t rnd = rng_philox ? cast_random_word(seed, offset, i) : 0u;
         store_cast(out, i, cast_from_f32(bits, c, rnd), elem);
     }
 }
@@ -251,6 +250,120 @@ __global__ void repack_kernel(RepackParams p) {
     }
 }
 
+// The same conversions for operands with a contiguous dimension (K, or M / N), four consecutive elements per thread, the
+// operand's orientation kept: src[batch][r][c] (rows r_stride apart, c contiguous) goes to dst[batch][r][c] with row pitch
+// dst_ld. The tf32 segments of modes 3 / 4 lie side by side along c when K is the contiguous dimension (seg_along_c), else
+// one below the other along r. The host takes this kernel when bases, pitches and extents are multiples of four elements.
+struct RepackVecParams {
+    const void* src;
+    void* dst;
+    uint64_t R, C;             // rows and contiguous extent (elements)
+    uint64_t r_stride;         // elements between source rows
+    uint64_t bstride[3];
+    uint32_t bsz[3];
+    uint64_t dst_ld, dst_batch;
+    uint64_t seg;              // elements (seg_along_c) or rows between the segments of modes 3 / 4
+    int seg_along_c;
+    int mode, src_elem, dtype, bias, inf_nan;
+    const uint32_t* pred;      // see GemmParams::pred
+    uint32_t pred_nonzero;
+};
+
+__global__ void repack_vec4_kernel(RepackVecParams p) {
+    if (p.pred != nullptr && ((*p.pred != 0u) != (p.pred_nonzero != 0u))) return;
+    const uint64_t c4 = p.C / 4;
+    const uint64_t per_batch = p.R * c4;
+    const uint64_t total = per_batch * p.bsz[0] * p.bsz[1] * p.bsz[2];
+    const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const uint64_t b = i / per_batch, rem = i % per_batch;
+        const uint64_t r = rem / c4, c = (rem % c4) * 4;
+        const uint64_t b0 = b % p.bsz[0], b1 = (b / p.bsz[0]) % p.bsz[1], b2 = b / (uint64_t(p.bsz[0]) * p.bsz[1]);
+        const uint64_t so = b0 * p.bstride[0] + b1 * p.bstride[1] + b2 * p.bstride[2] + r * p.r_stride + c;
+        const uint64_t d0 = b * p.dst_batch + r * p.dst_ld + c;
+        if (p.mode == 0) {
+            if (p.src_elem == 1) *reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(p.dst) + d0) = *reinterpret_cast<const uint32_t*>(static_cast<const uint8_t*>(p.src) + so);
+            else if (p.src_elem == 2) *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p.dst) + d0) = *reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(p.src) + so);
+            else *reinterpret_cast<uint4*>(static_cast<uint32_t*>(p.dst) + d0) = *reinterpret_cast<const uint4*>(static_cast<const uint32_t*>(p.src) + so);
+        } else if (p.mode == 1) {
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(static_cast<const uint8_t*>(p.src) + so);
+            const int ew = p.dtype == DT_FP8_143 ? 4 : 5;
+            uint32_t h[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = fp8_decode((w >> (8 * j)) & 0xFFu, ew, p.bias, p.inf_nan) >> 16;   // exact: <= 3 mantissa bits
+            *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p.dst) + d0) = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+        } else {
+            const uint4 v = *reinterpret_cast<const uint4*>(static_cast<const uint32_t*>(p.src) + so);
+            const uint32_t x[4] = {v.x, v.y, v.z, v.w};
+            uint32_t hi[4], lo[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                hi[j] = tf32_rne(x[j]);
+                lo[j] = 0;
+                if (p.mode != 2 && (x[j] & 0x7F800000u) != 0x7F800000u) lo[j] = tf32_rne(__float_as_uint(__uint_as_float(x[j]) - __uint_as_float(hi[j])));
+            }
+            uint32_t* d = static_cast<uint32_t*>(p.dst) + d0;
+            const uint4 vh = make_uint4(hi[0], hi[1], hi[2], hi[3]), vl = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            *reinterpret_cast<uint4*>(d) = vh;
+            if (p.mode != 2) {
+                const uint64_t step = p.seg_along_c ? p.seg : p.seg * p.dst_ld;
+                *reinterpret_cast<uint4*>(d + step) = (p.mode == 3) ? vh : vl;
+                *reinterpret_cast<uint4*>(d + 2 * step) = (p.mode == 3) ? vl : vh;
+            }
+        }
+    }
+}
+
+// fp32 / tf32 operands whose contiguous dimension is M or N: the tensor cores take 32-bit operands K-major only (an MN-major
+// tf32 tile gave wrong products), so these are transposed into a K-major copy while they are converted, through a
+// 32 x 33 shared-memory tile: reads run along the source's contiguous dimension, writes along K.
+// src element (k, mn) = src[batch_off + k * k_stride + mn]; dst[batch][mn][s * seg + k], s < 1 or 3.
+struct RepackTransposeParams {
+    const uint32_t* src;
+    uint32_t* dst;
+    uint64_t mn, k, k_stride;
+    uint64_t bstride[3];
+    uint32_t bsz[3];
+    uint64_t dst_ld, seg;
+    int mode;                  // 2 tf32 round, 3 / 4 the three tf32 segments of an fp32 operand (A / B order)
+};
+
+__global__ void repack_transpose_f32_kernel(RepackTransposeParams p) {
+    __shared__ uint32_t tile[32][33];
+    const uint64_t tiles_mn = (p.mn + 31) / 32, tiles_k = (p.k + 31) / 32;
+    const uint64_t per_batch = tiles_mn * tiles_k;
+    const uint64_t total = per_batch * p.bsz[0] * p.bsz[1] * p.bsz[2];
+    const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8 threads
+    for (uint64_t t = blockIdx.x; t < total; t += gridDim.x) {
+        const uint64_t b = t / per_batch, rem = t % per_batch;
+        const uint64_t k0 = (rem / tiles_mn) * 32, mn0 = (rem % tiles_mn) * 32;
+        const uint64_t b0 = b % p.bsz[0], b1 = (b / p.bsz[0]) % p.bsz[1], b2 = b / (uint64_t(p.bsz[0]) * p.bsz[1]);
+        const uint32_t* src = p.src + b0 * p.bstride[0] + b1 * p.bstride[1] + b2 * p.bstride[2];
+        __syncthreads();
+#pragma unroll
+        for (uint32_t j = ty; j < 32; j += 8) {
+            const uint64_t k = k0 + j, mn = mn0 + tx;
+            tile[j][tx] = (k < p.k && mn < p.mn) ? src[k * p.k_stride + mn] : 0u;
+        }
+        __syncthreads();
+#pragma unroll
+        for (uint32_t j = ty; j < 32; j += 8) {
+            const uint64_t mn = mn0 + j, k = k0 + tx;
+            if (mn >= p.mn || k >= p.k) continue;
+            const uint32_t x = tile[tx][j];
+            const uint32_t hi = tf32_rne(x);
+            uint32_t* d = p.dst + (b * p.mn + mn) * p.dst_ld + k;
+            d[0] = hi;
+            if (p.mode != 2) {
+                uint32_t lo = 0;
+                if ((x & 0x7F800000u) != 0x7F800000u) lo = tf32_rne(__float_as_uint(__uint_as_float(x) - __uint_as_float(hi)));
+                d[p.seg] = (p.mode == 3) ? hi : lo;
+                d[2 * p.seg] = (p.mode == 3) ? lo : hi;
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // General convolution lowering (any dim / stride / dilation / padding), mirroring RefIm2Col
 // (mme/mme_reference/im2col.cpp:54-172). Tensors are (C, W, H, D, B) with element strides.
@@ -377,7 +490,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, ReduceOut r) 
         if (f32_is_nan(bits)) bits = kF32CanonNan;
         if (r.has_cast) {
             if (r.cast.relu) bits = relu_bits(bits);
-            bits = cast_from_f32(bits, r.cast, r.rng_philox ? cast_random_word(r.cast.out_dtype, r.seed, r.offset, i) : 0u);
+            bits = cast_from_f32(bits, r.cast, r.rng_philox ? cast_random_word(r.seed, r.offset, i) : 0u);
         }
         uint64_t b = i / per;
         const uint64_t rem = i % per;
@@ -412,7 +525,7 @@ __global__ void splitk_reduce_vec4_kernel(const float* __restrict__ ws, ReduceOu
             if (f32_is_nan(bits[j])) bits[j] = kF32CanonNan;
             if (r.has_cast) {
                 if (r.cast.relu) bits[j] = relu_bits(bits[j]);
-                bits[j] = cast_from_f32(bits[j], r.cast, r.rng_philox ? cast_random_word(r.cast.out_dtype, r.seed, r.offset, i + j) : 0u);
+                bits[j] = cast_from_f32(bits[j], r.cast, r.rng_philox ? cast_random_word(r.seed, r.offset, i + j) : 0u);
             }
         }
         uint64_t b = i / per;

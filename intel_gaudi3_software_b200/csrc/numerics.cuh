@@ -615,11 +615,12 @@ MME_HD void philox_words4(uint64_t seed, uint64_t offset, uint64_t index4, uint3
     philox4x32_10(c, uint32_t(seed), uint32_t(seed >> 32));
     for (int j = 0; j < 4; ++j) w[j] = c[j] ? c[j] : 1u;
 }
-// 16-bit output types (bf16) discard 16 bits, so 16 random bits decide an element exactly: the element at stream
-// position pos takes half (pos & 1) of word ((pos >> 1) & 3) of block (pos >> 3) -- one Philox block serves EIGHT elements --
-// as the word (h << 16) | 0x8000. Rounding up when (discarded << 16) >= word then happens with probability
-// discarded / 2^16 exactly, and never for an exactly representable value. The third counter word is 1, which keeps this
-// stream apart from the 32-bit one above.
+// The stochastic casts draw 16 random bits per element: the element at stream position pos takes half (pos & 1) of word
+// ((pos >> 1) & 3) of block (pos >> 3) -- one Philox block serves EIGHT elements -- as the word (h << 16) | 0x8000. A bf16
+// output discards 16 bits, so rounding up when (discarded << 16) >= word happens with probability discarded / 2^16
+// exactly; an fp8 output discards 20 bits or more and its probability is the discarded fraction rounded to 16 bits (off by
+// at most 2^-17, unbiased over the lower bits). An exactly representable value never moves. The third counter word is 1,
+// which keeps this stream apart from the generator's 32-bit one above.
 MME_HD uint32_t philox_half(uint64_t seed, uint64_t offset, uint64_t index) {
     const uint64_t pos = offset + index, ctr = pos >> 3;
     uint32_t c[4] = {uint32_t(ctr), uint32_t(ctr >> 32), 1u, 0u};
@@ -648,10 +649,8 @@ MME_HD void philox_halves4(uint64_t seed, uint64_t offset, uint64_t index4, uint
         w[2 * j + 1] = (c[first + j] & 0xFFFF0000u) | 0x8000u;
     }
 }
-// The random word of one element of a cast: which of the two streams applies follows from the output type.
-MME_HD uint32_t cast_random_word(int out_dtype, uint64_t seed, uint64_t offset, uint64_t index) {
-    return out_dtype == DT_BF16 ? philox_half(seed, offset, index) : philox_word(seed, offset, index);
-}
+// The random word of one element of a stochastic cast (every output type).
+MME_HD uint32_t cast_random_word(uint64_t seed, uint64_t offset, uint64_t index) { return philox_half(seed, offset, index); }
 
 // ---------------------------------------------------------------------------------------------
 // Element comparison of the reference's TensorComparator
