@@ -39,6 +39,7 @@ struct Tuning {
     int tma_store = -1;       // 0: direct stores even where a TMA store applies
     int host_pipeline = -1;   // 0: host-tensor GEMMs are staged whole instead of pipelined
     int tile_n = -1;          // CTA-pair kernel: forced tile width (a multiple of 32 in [32, 256])
+    int stream_k = -1;        // 0: never cut the tiles of a ragged last wave along K; 1: cut them whenever there is such a wave
 };
 static int env_int(const char* name, int dflt) {
     const char* e = getenv(name);
@@ -72,6 +73,10 @@ struct mmeb200_ctx {
     uint64_t launches = 0;
     void* aux = nullptr;            // dense copies of strided convolution tensors (outlives the per-call arena)
     size_t aux_bytes = 0;
+    // cut tail of the CTA-pair kernel: slots for the partial sums of the cut tiles' pieces, one flag word per epilogue warp and slot
+    float* sk_ws = nullptr;
+    uint32_t* sk_flags = nullptr;
+    uint32_t sk_slots_cap = 0, sk_gen = 0;
 
     int fail(int code, const char* fmt, ...) {
         char buf[512];
@@ -505,6 +510,62 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
         TRY(arena_alloc(c, &ws, size_t(split) * p.batches * j.M * j.N * 4));
         p.out = ws;
     }
+    // a tile with few k blocks spends longer in its epilogue than in its MMAs: give it eight epilogue warps; and so does
+    // the general cast (stochastic rounding, fp8 output), tens of instructions per element
+    bool two_groups = (p.num_k_blocks + split - 1) / split <= 12 || (split == 1 && (p.epi_mode == EPI_GENERIC || p.epi_mode == EPI_FP8_HW));
+    if (tune.epi_groups > 0) two_groups = tune.epi_groups == 2;
+    if (use_pair) {   // plan with what both variants of the pair kernel hold at once
+        const uint64_t cap2 = uint64_t(gemm_pair_capacity(launch_env(c), j.kind, 2));
+        if (cap2) units = std::min(units, cap2);
+    }
+    // Cut tail: with whole tiles only, `tiles % units` tiles make a last wave that leaves pairs idle (1024 x 8192 outputs:
+    // 128 tiles on 74 pairs, 1.73 waves). Each of those tiles is cut along K into a head, computed by a pair of its own, and
+    // pieces that the remaining pairs share; the head's pair adds the pieces' sums and finishes the tile (PairSchedule,
+    // gemm_sm100_pair.cuh). Head and piece lengths are the ones that finish earliest; the cut pays when that beats a whole
+    // tile's k blocks by a margin: every piece costs 128 KB per CTA written and read again through L2, beside the operands.
+    uint64_t launch_pairs = tiles * split;
+    if (use_pair && split == 1 && !peer && tune.stream_k != 0 && units > 1) {
+        const uint64_t rem = tiles % units, waves = tiles / units + 1, helpers = units - rem;
+        const uint32_t nkb = p.num_k_blocks;
+        uint32_t best_head = 0, best_piece = 0, best_pieces = 0;
+        uint64_t best_cost = nkb;
+        for (uint32_t head = std::max(4u, uint32_t((rem * nkb + units - 1) / units)); rem != 0 && head < nkb; ++head) {
+            const uint32_t rest = nkb - head;
+            const uint32_t pieces = (rest + head - 1) / head, piece = (rest + pieces - 1) / pieces;
+            if (rem * pieces > 224 || piece < 2) break;
+            // a piece's pair is busy for the piece's k blocks or, if longer, for the epilogue that writes its sums
+            // (about sixteen k blocks' time, measured)
+            const uint64_t helper_time = ((rem * pieces + helpers - 1) / helpers) * std::max(piece, 16u);
+            const uint64_t cost = std::max<uint64_t>(head, helper_time) + 4;
+            if (cost < best_cost || (tune.stream_k > 0 && best_head == 0)) {   // the knob takes any cut, the planner one that pays
+                best_cost = std::min(cost, uint64_t(nkb)); best_head = head; best_piece = piece; best_pieces = pieces;
+            }
+            if (((rem * pieces + helpers - 1) / helpers) * piece <= head) break;   // longer heads only finish later
+        }
+        const bool pays = best_head && (nkb - best_cost) * 100 >= 10 * waves * nkb;
+        if (best_head && (pays || tune.stream_k > 0)) {
+            // eight epilogue warps: adding a slot's sums is bound by the loads a warp keeps in flight
+            if (tune.epi_groups <= 0) two_groups = true;
+            const uint32_t slots = uint32_t(rem) * best_pieces;
+            if (c->sk_slots_cap < slots) {
+                if (c->sk_ws) { CUDA_OK(c, cudaStreamSynchronize(c->stream)); cudaFree(c->sk_ws); cudaFree(c->sk_flags); c->sk_ws = nullptr; c->sk_flags = nullptr; }
+                const uint32_t cap = std::max(slots, 74u);
+                CUDA_OK(c, cudaMalloc(&c->sk_ws, size_t(cap) * 2 * kSkSlotFloats * sizeof(float)));
+                CUDA_OK(c, cudaMalloc(&c->sk_flags, size_t(cap) * 2 * kSkFlagsPerCta * sizeof(uint32_t)));
+                CUDA_OK(c, cudaMemsetAsync(c->sk_flags, 0, size_t(cap) * 2 * kSkFlagsPerCta * sizeof(uint32_t), c->stream));
+                c->sk_slots_cap = cap;
+                c->sk_gen = 0;
+            }
+            p.sk_tiles = uint32_t(rem);
+            p.sk_head = best_head;
+            p.sk_piece = best_piece;
+            p.sk_pieces = best_pieces;
+            p.sk_ws = c->sk_ws;
+            p.sk_flags = c->sk_flags;
+            p.sk_gen = ++c->sk_gen;
+            launch_pairs = units;   // heads on the first pairs, pieces on the others
+        }
+    }
     if (j.a_im2col) p.tm_a = j.a_map;
     else if (!j.a.mn_major) TRY(encode_tiled(c, &p.tm_a, j.a, p.block_k, kBlockM));
     else TRY(encode_tiled(c, &p.tm_a, j.a, kRowBytes / elem, p.block_k));
@@ -528,12 +589,7 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     const unsigned grid = unsigned(std::min<uint64_t>(tiles * split, uint64_t(c->sm_count)));
     int rc;
     if (use_pair) {
-        const uint64_t pair_tiles = tiles * split;
-        // a tile with few k blocks spends longer in its epilogue than in its MMAs: give it eight epilogue warps
-        const uint32_t kb_per_tile = (p.num_k_blocks + split - 1) / split;
-        // ... and so does the general cast (stochastic rounding, fp8 output), hundreds of instructions per element
-        bool two_groups = kb_per_tile <= 12 || (split == 1 && (p.epi_mode == EPI_GENERIC || p.epi_mode == EPI_FP8_HW));
-        if (tune.epi_groups > 0) two_groups = tune.epi_groups == 2;
+        const uint64_t pair_tiles = launch_pairs;
         rc = launch_status(c, launch_gemm_pair(launch_env(c), j.kind, two_groups ? 2 : 1, p, pair_tiles));
     } else {
         rc = launch_status(c, launch_gemm_single(launch_env(c), j.kind, block_n, p, grid));
@@ -811,7 +867,9 @@ static int run_cast(mmeb200_ctx* c, void* out, uint32_t* acc, uint64_t n, const 
         else if (cast_is_fp8_hw(s)) {
             tier.kind = CAST_FP8_HW;
             tier.hw = fp8_hw_cast(s);
-        } else if ((!philox || (offset & 3u) == 0) && (s.out_dtype == DT_BF16 || (dtype_is_fp8(s.out_dtype) && !s.ftz && !s.sftz)))
+        } else if (philox && s.rm == RM_SR && (offset & 7u) == 0 && !s.ftz && (s.out_dtype == DT_BF16 || (dtype_is_fp8(s.out_dtype) && !s.sftz)))
+            tier.kind = CAST_SR8;
+        else if ((!philox || (offset & 3u) == 0) && (s.out_dtype == DT_BF16 || (dtype_is_fp8(s.out_dtype) && !s.ftz && !s.sftz)))
             tier.kind = CAST_FLAT;
         cast_kernel<<<grid_for((n + 15) / 16, 256, c->sm_count), 256, 0, c->stream>>>(out, acc, n, s, philox ? 1 : 0, cp ? cp->rng_seed : 0, offset, tier);
         c->launches++;
@@ -1075,6 +1133,7 @@ int mmeb200_create(mmeb200_ctx** out_ctx, int chip, int device, unsigned seed, u
     c->tune.tma_store = getenv("MME_B200_NO_TMA_STORE") ? 0 : -1;
     c->tune.host_pipeline = getenv("MME_B200_NO_HOST_PIPELINE") ? 0 : -1;
     c->tune.tile_n = env_int("MME_B200_TILE_N", -1);
+    c->tune.stream_k = env_int("MME_B200_STREAM_K", -1);
     if (cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) != cudaSuccess || cudaMalloc(&c->d_status, 64) != cudaSuccess ||
         cudaMallocHost(&c->h_status, 64) != cudaSuccess || cudaEventCreate(&c->ev0) != cudaSuccess || cudaEventCreate(&c->ev1) != cudaSuccess) {
         delete c;
@@ -1107,6 +1166,8 @@ void mmeb200_destroy(mmeb200_ctx* c) {
     }
     for (auto& b : c->arena) cudaFree(b.ptr);
     if (c->aux) cudaFree(c->aux);
+    if (c->sk_ws) cudaFree(c->sk_ws);
+    if (c->sk_flags) cudaFree(c->sk_flags);
     if (c->d_status) cudaFree(c->d_status);
     if (c->h_status) cudaFreeHost(c->h_status);
     if (c->d_jump) cudaFree(c->d_jump);
@@ -1137,7 +1198,7 @@ int mmeb200_set_option(mmeb200_ctx* c, const char* name, int value) {
     struct { const char* name; int Tuning::*field; } const table[] = {
         {"pair", &Tuning::pair}, {"block_n", &Tuning::block_n}, {"split_k", &Tuning::split_k}, {"epi_groups", &Tuning::epi_groups},
         {"raster_gm", &Tuning::raster_gm}, {"tma_store", &Tuning::tma_store}, {"host_pipeline", &Tuning::host_pipeline},
-        {"tile_n", &Tuning::tile_n}};
+        {"tile_n", &Tuning::tile_n}, {"stream_k", &Tuning::stream_k}};
     for (const auto& t : table)
         if (strcmp(t.name, name) == 0) {
             c->tune.*(t.field) = value < 0 ? -1 : value;

@@ -40,7 +40,9 @@ enum : uint32_t {
     WAIT_MMA_FULL = 2,
     WAIT_MMA_TMEM_EMPTY = 3,
     WAIT_EPILOGUE_TMEM_FULL = 4,
-    SMEM_MISALIGNED = 5
+    SMEM_MISALIGNED = 5,
+    WAIT_STREAMK_PARTIAL = 6,
+    CUT_TAIL_WITHOUT_HELPERS = 7
 };
 
 struct ConvGeom {
@@ -102,7 +104,70 @@ struct GemmParams {
     // (fp8 codes that the tensor cores would read differently) and lets the device pick, with no host round trip.
     const uint32_t* pred;
     uint32_t pred_nonzero;
+    // Cut tail of the CTA-pair kernel (split_k == 1). With whole tiles only, the last `tiles % pairs` tiles make a wave that
+    // leaves pairs idle. The planner cuts each of those sk_tiles tiles (the last ones of the raster order) along K into a
+    // head of sk_head k blocks and sk_pieces further pieces of sk_piece k blocks. Pair t < sk_tiles computes the head of cut
+    // tile t; the other pairs share the pieces, last piece first (PairSchedule); every pair then goes on to its whole tiles.
+    // The sums travel down a tile's pieces: the pair with piece q waits for slot (tile, q + 1) unless q is the last piece,
+    // adds it to its raw fp32 accumulator, writes the result to slot (tile, q) = tile * sk_pieces + q - 1 of sk_ws and then
+    // stores sk_gen to its epilogue warps' words of sk_flags; the pair with the head waits for slot (tile, 1), adds it and
+    // does the tile's epilogue. Nobody waits for a pair that itself waits for work that has not started.
+    uint32_t sk_tiles;       // 0: every tile is computed whole by one pair
+    uint32_t sk_head, sk_piece, sk_pieces;
+    float* sk_ws;            // [slot][CTA of the pair][column 0..255][row 0..127] floats: 128 KB per CTA
+    uint32_t* sk_flags;      // [slot][CTA of the pair][16]: one word per epilogue warp of the writer
+    uint32_t sk_gen;         // differs from every earlier launch that used the same flags; never 0
 };
+constexpr uint32_t kSkSlotFloats = 8 * kBlockM * 32;   // one CTA's 128 x 256 partial accumulator
+constexpr uint32_t kSkFlagsPerCta = 16;
+
+// What the pair with the head of a cut tile adds to its accumulator before the cast: this CTA's part of the slot `ws` when
+// count != 0. col0: first column of the warp's share within the tile.
+struct SkFix {
+    const float* ws;
+    uint32_t count;
+    uint32_t col0;
+};
+// 32 accumulator columns of this lane's row (tile column `col`, a multiple of 32) plus the slot's values for them. A slot
+// holds its CTA's 128 x 256 sums column by column, so the 32 lanes of a warp (32 consecutive rows) read and write 128
+// consecutive bytes per column. The loads are issued before the wait for the accumulator's own load.
+__device__ __forceinline__ void tmem_ld_wait_add(uint32_t (&v)[32], const SkFix& fix, uint32_t col, uint32_t row_in_cta) {
+    if (fix.count) {
+        const float* src = fix.ws + uint64_t(col) * kBlockM + row_in_cta;
+        float w[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) w[j] = __ldcg(src + j * kBlockM);   // written by another SM during this launch: read past L1
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + w[j]);
+    } else {
+        tmem_ld_wait();
+    }
+}
+// A piece of a cut tile: this warp's 32 rows x tile_cols raw accumulator columns, plus the running sum of the pieces
+// after it (`above`, nullptr for the last piece), into its CTA's slot.
+static __device__ __noinline__ void epilogue_partial(float* slot, const float* above, uint32_t col0, uint32_t tile_cols, uint32_t tmem_acc,
+                                                     uint32_t row_in_cta) {
+#pragma unroll 1
+    for (uint32_t c0 = 0; c0 < tile_cols; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_acc + c0, v);
+        const uint64_t at = uint64_t(col0 + c0) * kBlockM + row_in_cta;
+        if (above) {
+            float w[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) w[j] = __ldcg(above + at + j * kBlockM);   // in flight while the accumulator arrives
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + w[j]);
+        } else {
+            tmem_ld_wait();
+        }
+        float* dst = slot + at;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) dst[j * kBlockM] = __uint_as_float(v[j]);
+    }
+}
 
 __device__ __forceinline__ bool launch_is_predicated_off(const uint32_t* pred, uint32_t pred_nonzero) {
     return pred != nullptr && ((*pred != 0u) != (pred_nonzero != 0u));
@@ -158,6 +223,22 @@ __device__ __forceinline__ uint32_t epilogue_prepare(uint32_t acc, const GemmPar
 template <int RM>
 __device__ __forceinline__ void epilogue_bf16_flat(uint32_t (&v)[32], const GemmParams& p, uint64_t flat_index) {
     const bool clip = p.cast.clip, ftz = p.cast.ftz, clip_inf_in = p.cast.clip_inf_in;
+    if constexpr (RM == RM_SR) {
+        if (p.rng_philox && !ftz && !p.cast.relu) {
+            // the rounding as one addition per element (sr_bf16_group8); NaN needs no canonical form, every NaN gives 0x7FFF
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                uint32_t c[4], x[8], w[4];
+                philox_block8(p.rng_seed, p.rng_offset, flat_index + 8 * g, c);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] = __float_as_uint(__uint_as_float(v[8 * g + e]) * p.scale);
+                sr_bf16_group8(x, c, clip, clip_inf_in, w);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[4 * g + e] = w[e];
+            }
+            return;
+        }
+    }
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
         uint32_t rnd[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u}, o[8];
@@ -175,6 +256,23 @@ template <int RM>
 __device__ __forceinline__ void epilogue_fp8_flat(uint32_t (&v)[32], const GemmParams& p, uint64_t flat_index) {
     const int exp_width = p.cast.exp_width, bias = p.cast.bias, mode = p.cast.mode;
     const bool clip = p.cast.clip, clip_inf_in = p.cast.clip_inf_in;
+    if constexpr (RM == RM_SR) {
+        if (p.rng_philox && !p.cast.relu) {
+            // the rounding as one addition per element (sr_fp8_group8); the accumulator's NaN is the positive canonical one
+            const Fp8SrSpec sp = fp8_sr_spec(exp_width, bias, mode);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                uint32_t c[4], x[8], w[2];
+                philox_block8(p.rng_seed, p.rng_offset, flat_index + 8 * g, c);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] = __float_as_uint(__uint_as_float(v[8 * g + e]) * p.scale);
+                sr_fp8_group8(x, c, sp, exp_width, bias, mode, clip, clip_inf_in, true, w);
+                v[2 * g] = w[0];
+                v[2 * g + 1] = w[1];
+            }
+            return;
+        }
+    }
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
         uint32_t rnd[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u}, o[8];
@@ -259,10 +357,9 @@ __device__ __forceinline__ void epilogue_convert(uint32_t (&v)[32], const GemmPa
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 x[e] = __uint_as_float(v[4 * q + e]) * p.scale;
-                if (x[e] != x[e]) x[e] = __uint_as_float(kF32CanonNan);   // the accumulator's NaN is canonical (positive)
                 if (relu) x[e] = x[e] > 0.0f ? x[e] : 0.0f;          // NaN and -0 become +0, as std::max(0.f, x)
             }
-            v[q] = f32x4_to_fp8_hw(x, p.hw);   // word q lies below every value still to be read
+            v[q] = f32x4_to_fp8_hw(x, p.hw, true);   // the accumulator's NaN is canonical (positive); word q lies below every value still to be read
         }
     } else {
         // bf16 in the other rounding modes: some twenty instructions per element, inlined on the accumulator registers
@@ -505,7 +602,7 @@ __device__ __forceinline__ void store_row32(const uint32_t (&v)[32], uint8_t* ds
 // them. m0 is the first row of the CTA's 128-row block, n0 the first column.
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tile_cols, uint32_t m0, uint32_t n0, uint32_t batch, uint32_t split,
                                               uint32_t tmem_acc, uint8_t* stage_out, uint32_t& store_buf, uint32_t sub, uint32_t lane,
-                                              uint32_t out_elem) {
+                                              uint32_t out_elem, const SkFix& fix = SkFix{nullptr, 0u, 0u}) {
     const uint32_t row = m0 + sub * 32 + lane;
     uint32_t bi[3];
     {
@@ -552,7 +649,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tile
             for (uint32_t l = 0; l < lds_per_chunk; ++l) {
                 uint32_t v[32];
                 tmem_ld_32x32b_x32(tmem_acc + ch * cols_per_chunk + l * 32, v);
-                tmem_ld_wait();
+                tmem_ld_wait_add(v, fix, fix.col0 + ch * cols_per_chunk + l * 32, sub * 32 + lane);
                 epilogue_convert(v, p, out_elem, flat_row + col0 + l * 32);
                 if (out_elem == 4) {
 #pragma unroll
@@ -583,7 +680,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tile
     for (uint32_t c0 = done_cols; c0 < tile_cols; c0 += 32) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(tmem_acc + c0, v);
-        tmem_ld_wait();
+        tmem_ld_wait_add(v, fix, fix.col0 + c0, sub * 32 + lane);
         const uint32_t col0 = n0 + c0;
         if (row >= p.M || col0 >= p.N) continue;
         const uint32_t ncols = min(32u, p.N - col0);

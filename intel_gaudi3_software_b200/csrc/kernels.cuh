@@ -21,7 +21,9 @@ __device__ __forceinline__ void store_cast(void* out, uint64_t i, uint32_t v, in
 // Which body converts a group of four values (uniform per launch): the general cast, or one of the forms the GEMM
 // epilogue uses -- the hardware bf16 conversion (round-to-nearest-even, no flags: NaN -> 0x7FFF, denormals kept), the
 // hardware fp8 conversion (f32x4_to_fp8_hw) or the straight-line casts (f32_to_bf16_flat / f32_to_fp8_flat).
-enum : int { CAST_GENERAL = 0, CAST_BF16_RNE = 1, CAST_FP8_HW = 2, CAST_FLAT = 3 };
+// CAST_SR8: Philox stochastic rounding of groups of EIGHT elements, one Philox block and one addition per element
+// (sr_bf16_group8 / sr_fp8_group8), when the stream offset keeps the groups aligned.
+enum : int { CAST_GENERAL = 0, CAST_BF16_RNE = 1, CAST_FP8_HW = 2, CAST_FLAT = 3, CAST_SR8 = 4 };
 struct CastTier {
     int kind;
     Fp8HwCast hw;   // CAST_FP8_HW
@@ -78,6 +80,60 @@ __global__ void cast_kernel(void* __restrict__ out, uint32_t* __restrict__ acc, 
     const uint64_t chunks = ((reinterpret_cast<uintptr_t>(acc) | reinterpret_cast<uintptr_t>(out)) & 15) ? 0 : n / (4 * kChunk);   // vector path needs aligned bases
     const bool block_rng = rng_philox && (offset & 3u) == 0;
     const uint32_t lane = threadIdx.x & 31;
+    if (tier.kind == CAST_SR8) {
+        // lane l takes the groups of eight l and l + 32 of a warp's 64: two 16-byte loads and one 16- or 8-byte store per group
+        const Fp8SrSpec sp = fp8_sr_spec(c.exp_width, c.bias, c.mode);
+        constexpr uint64_t kChunk8 = 2 * 32;
+        const uint64_t chunks8 = chunks ? n / (8 * kChunk8) : 0;
+        for (uint64_t ch = tid >> 5; ch < chunks8; ch += stride >> 5) {
+            uint32_t b[2][8];
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+                const uint64_t q = ch * kChunk8 + g * 32 + lane;
+                const uint4 v0 = reinterpret_cast<const uint4*>(acc)[2 * q], v1 = reinterpret_cast<const uint4*>(acc)[2 * q + 1];
+                b[g][0] = v0.x; b[g][1] = v0.y; b[g][2] = v0.z; b[g][3] = v0.w;
+                b[g][4] = v1.x; b[g][5] = v1.y; b[g][6] = v1.z; b[g][7] = v1.w;
+            }
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+                const uint64_t q = ch * kChunk8 + g * 32 + lane;   // elements 8q .. 8q+7
+                if (c.relu) {
+                    bool changed = false;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint32_t r = relu_bits(b[g][j]);
+                        changed |= r != b[g][j];
+                        b[g][j] = r;
+                    }
+                    if (changed) {
+                        reinterpret_cast<uint4*>(acc)[2 * q] = make_uint4(b[g][0], b[g][1], b[g][2], b[g][3]);
+                        reinterpret_cast<uint4*>(acc)[2 * q + 1] = make_uint4(b[g][4], b[g][5], b[g][6], b[g][7]);
+                    }
+                }
+                uint32_t blk[4];
+                philox_block8(seed, offset, q * 8, blk);
+                if (elem == 2) {
+                    uint32_t w[4];
+                    sr_bf16_group8(b[g], blk, c.clip, c.clip_inf_in, w);
+                    reinterpret_cast<uint4*>(out)[q] = make_uint4(w[0], w[1], w[2], w[3]);
+                } else {
+                    uint32_t w[2];
+                    sr_fp8_group8(b[g], blk, sp, c.exp_width, c.bias, c.mode, c.clip, c.clip_inf_in, false, w);
+                    reinterpret_cast<uint2*>(out)[q] = make_uint2(w[0], w[1]);
+                }
+            }
+        }
+        for (uint64_t i = chunks8 * kChunk8 * 8 + tid; i < n; i += stride) {
+            uint32_t bits = acc[i];
+            if (c.relu) {
+                const uint32_t r = relu_bits(bits);
+                if (r != bits) acc[i] = r;
+                bits = r;
+            }
+            store_cast(out, i, cast_from_f32(bits, c, cast_random_word(seed, offset, i)), elem);
+        }
+        return;
+    }
     for (uint64_t ch = tid >> 5; ch < chunks; ch += stride >> 5) {
         uint32_t b[kCastGroups][4];
 #pragma unroll

@@ -68,6 +68,26 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     }
 }
 
+// A word in global memory that another CTA of the same launch sets to `want` (st_release_gpu): wait for it, for at most
+// `limit_ns` nanoseconds. Returns false when the limit ran out.
+__device__ __forceinline__ void st_release_gpu(uint32_t* flag, uint32_t value) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(value) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* flag) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    return v;
+}
+__device__ __forceinline__ bool flag_wait_bounded(const uint32_t* flag, uint32_t want, uint64_t limit_ns) {
+    if (ld_acquire_gpu(flag) == want) return true;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (true) {
+        if (ld_acquire_gpu(flag) == want) return true;
+        if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > limit_ns) return false;
+    }
+}
+
 // ---------------------------------------------------------------- TMA (tensor maps live in __grid_constant__ params)
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

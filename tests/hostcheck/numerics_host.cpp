@@ -128,6 +128,42 @@ void hc_philox_halves(uint64_t seed, uint64_t offset, uint64_t index8, uint32_t*
     for (int i = 0; i < 8; i++) w8[i] = a[i];
     for (int i = 0; i < 4; i++) { w4a[i] = b[i]; w4b[i] = c[i]; }
 }
+// Stochastic rounding of groups of eight with their raw Philox blocks (blocks: 4 words per group): the addition form
+// (sr_bf16_group8 / sr_fp8_group8) into `fast`, the straight-line cast element by element into `flat`.
+void hc_sr_groups(const uint32_t* in, const uint32_t* blocks, size_t groups, int out_dtype, int exp_width, int bias, int mode, int clip,
+                  int clip_inf_in, int canon_nan, uint8_t* fast, uint8_t* flat)
+{
+    const Fp8SrSpec sp = fp8_sr_spec(exp_width, bias, mode);
+    for (size_t g = 0; g < groups; g++) {
+        const uint32_t* x = in + 8 * g;
+        const uint32_t c[4] = {blocks[4 * g], blocks[4 * g + 1], blocks[4 * g + 2], blocks[4 * g + 3]};
+        if (out_dtype == DT_BF16) {
+            uint32_t w[4];
+            sr_bf16_group8(x, c, clip, clip_inf_in, w);
+            for (int e = 0; e < 8; e++) {
+                const uint32_t v = (w[e >> 1] >> (16 * (e & 1))) & 0xFFFFu;
+                const uint32_t r = f32_to_bf16_flat<RM_SR>(x[e], philox_block8_word(c, e), clip, false, clip_inf_in);
+                fast[16 * g + 2 * e] = uint8_t(v); fast[16 * g + 2 * e + 1] = uint8_t(v >> 8);
+                flat[16 * g + 2 * e] = uint8_t(r); flat[16 * g + 2 * e + 1] = uint8_t(r >> 8);
+            }
+        } else {
+            uint32_t w[2];
+            sr_fp8_group8(x, c, sp, exp_width, bias, mode, clip, clip_inf_in, canon_nan, w);
+            for (int e = 0; e < 8; e++) {
+                const uint32_t xin = (canon_nan && f32_is_nan(x[e])) ? kF32CanonNan : x[e];
+                fast[8 * g + e] = uint8_t(w[e >> 2] >> (8 * (e & 3)));
+                flat[8 * g + e] = uint8_t(f32_to_fp8_flat<RM_SR>(xin, exp_width, bias, philox_block8_word(c, e), mode, clip, clip_inf_in));
+            }
+        }
+    }
+}
+void hc_philox_block8(uint64_t seed, uint64_t offset, uint64_t index8, uint32_t* c4, uint32_t* words8)
+{
+    uint32_t c[4];
+    philox_block8(seed, offset, index8, c);
+    for (int i = 0; i < 4; i++) c4[i] = c[i];
+    for (int e = 0; e < 8; e++) words8[e] = philox_block8_word(c, e);
+}
 void hc_philox_block(uint32_t* c, uint32_t k0, uint32_t k1)
 {
     uint32_t s[4] = {c[0], c[1], c[2], c[3]};

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 
 import intel_gaudi3_software_b200 as pkg
-from intel_gaudi3_software_b200 import abi
+from intel_gaudi3_software_b200 import abi, workloads
 from intel_gaudi3_software_b200.abi import make_tensor as T
 import util
 from golden.make_golden import GEMM_CASES
@@ -61,6 +61,8 @@ KERNEL_VARIANTS = {
     "pair, 224-wide tiles": {"pair": 1, "tile_n": 224},
     "pair, 160-wide tiles, eight epilogue warps": {"pair": 1, "tile_n": 160, "epi_groups": 2},
     "pair, 96-wide tiles": {"pair": 1, "tile_n": 96},
+    "pair, stream-K tail": {"pair": 1, "split_k": 1, "stream_k": 1},
+    "pair, stream-K tail, eight epilogue warps, direct stores": {"pair": 1, "split_k": 1, "stream_k": 1, "epi_groups": 2, "tma_store": 0},
     "single CTA, 256 wide": {"pair": 0},
     "single CTA, 128 wide": {"block_n": 128},
     "single CTA, no TMA stores": {"pair": 0, "tma_store": 0},
@@ -81,6 +83,56 @@ def test_every_kernel_variant_matches_the_oracle(calc, best_oracle, variant):
     finally:
         for k in knobs:
             calc.set_option(k, -1)
+
+
+@pytest.mark.parametrize("M,N,K,op,batch", [(512, 768, 2048, abi.OP_AB, ()), (1024, 512, 1536, abi.OP_ATB, ()), (300, 700, 1100, abi.OP_ABT, ()),
+                                             (256, 256, 1024, abi.OP_AB, (3,)), (2560, 2048, 1024, abi.OP_AB, ())])
+def test_stream_k_tail(calc, best_oracle, M, N, K, op, batch):
+    """Tiles of a ragged last wave are cut along K into slices that go round the CTA pairs; the pair with a tile's first slice
+    adds the others' partial sums: against the oracle, equal run to run, and within the accumulation tolerance of the uncut
+    launch. The last shape has whole tiles (80 on 74 pairs) besides the cut ones."""
+    try:
+        calc.set_option("pair", 1)
+        calc.set_option("split_k", 1)
+        calc.set_option("stream_k", 1)
+        cut, _ = run_case(calc, best_oracle, M, N, K, op, batch=batch, seed=11)
+        again, _ = run_case(calc, best_oracle, M, N, K, op, batch=batch, seed=11)
+        calc.set_option("stream_k", 0)
+        whole, _ = run_case(calc, best_oracle, M, N, K, op, batch=batch, seed=11)
+    finally:
+        calc.set_option("pair", -1)
+        calc.set_option("split_k", -1)
+        calc.set_option("stream_k", -1)
+    assert (cut.view(np.uint32) == again.view(np.uint32)).all()
+    assert (cut != whole).any()        # the summation order differs, so some last bits do
+    assert np.abs(cut.astype(np.float64) - whole).max() <= util.ACC_TOL * K / 4
+
+
+def test_stream_k_tail_at_the_sharded_headline_shape(calc):
+    """1024 x 8192 x 8192 fp8 -> bf16 (one rank's rows of the 8192^3 product on eight GPUs): 128 tiles on 74 pairs, the last
+    54 cut into four slices each. Against the uncut launch: bf16 outputs equal or one step apart."""
+    rng = np.random.default_rng(5)
+    M, N, K = 1024, 8192, 8192
+    a = workloads.quantise_fp8(rng.standard_normal(M * K).astype(np.float32), abi.FP8_143, 7)
+    b = workloads.quantise_fp8(rng.standard_normal(N * K).astype(np.float32), abi.FP8_143, 7)
+    outs = []
+    for knob in (1, 0):
+        calc.set_option("stream_k", knob)
+        calc.set_option("host_pipeline", 0)   # one launch over all 1024 rows, not a pipeline of row blocks
+        try:
+            o = np.zeros(M * N, np.uint16)
+            calc.do_batch_gemm(T(o, abi.BF16, [N, M]), T(a, abi.FP8_143, [K, M], fp_bias=7, inf_nan_mode=abi.INFNAN_MINIMAL),
+                               T(b, abi.FP8_143, [K, N], fp_bias=7, inf_nan_mode=abi.INFNAN_MINIMAL), abi.OP_ABT,
+                               cast=abi.make_cast_params(abi.RM_NE))
+            outs.append(o)
+        finally:
+            calc.set_option("stream_k", -1)
+            calc.set_option("host_pipeline", -1)
+    cut, whole = (workloads.bf16_to_f32(o) for o in outs)
+    differ = outs[0] != outs[1]
+    assert 0 < differ.mean() < 0.02, differ.mean()
+    # one bf16 step apart at most (values next to zero may differ in sign: an absolute allowance far below the outputs' spread)
+    assert (np.abs(cut - whole) <= np.maximum(np.abs(cut), np.abs(whole)) * 2.0 ** -7 + 1e-4 * whole.std()).all()
 
 
 @pytest.mark.parametrize("op", [abi.OP_AB, abi.OP_ABT, abi.OP_ATB, abi.OP_ATBT])

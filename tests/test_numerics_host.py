@@ -182,6 +182,64 @@ def test_philox_half_stream_for_16_bit_outputs(hc):
     assert ((w32 >> 16) != (w[:64] >> 16)).mean() > 0.9
 
 
+def sr_inputs(discard_bits, e_small, e_top):
+    """fp32 values in groups of eight with a raw Philox-like block each: every exponent and sign, mantissas with structured
+    and random low parts, and random halves placed at, just below and just above the value's own discarded bits (the
+    decision's change point), besides uniform ones. Some groups hold a value near the top of the range, Inf or NaN."""
+    rng = np.random.default_rng(23)
+    n = 1 << 21
+    sign = rng.integers(0, 2, n, dtype=np.uint64) << 31
+    ex = rng.integers(0, 256, n, dtype=np.uint64)
+    where = rng.integers(0, 4, n)
+    ex = np.where(where == 0, rng.integers(e_small - 9, e_small + 3, n).astype(np.uint64), ex)   # the output's subnormal range and below
+    ex = np.where(where == 1, rng.integers(e_top - 2, e_top + 2, n).astype(np.uint64), ex)       # its largest binade and the overflow
+    ex = np.clip(ex, 0, 255).astype(np.uint64) << 23
+    man = rng.integers(0, 1 << 23, n, dtype=np.uint64)
+    kind = rng.integers(0, 6, n)
+    man = np.where(kind == 0, man & ~np.uint64((1 << discard_bits) - 1), man)          # exactly representable
+    man = np.where(kind == 1, man | np.uint64((1 << discard_bits) - 1), man)           # all discarded bits set
+    man = np.where(kind == 2, (man & ~np.uint64((1 << discard_bits) - 1)) | np.uint64(1), man)
+    bits = (sign | ex | man).astype(np.uint32)
+    special = np.array([0, 0x80000000, 0x7F800000, 0xFF800000, 0x7FC00000, 0xFFC00001, 0x7FFFFFFF, 0xFFFFFFFF, 1, 0x007FFFFF, 0x7F7FFFFF,
+                        0xFF7FFFFF, 0x7F7F0000, 0x7F7F0001, 0x7F7EFFFF], dtype=np.uint32)
+    bits[: special.size * 8 : 8] = special                                             # one special value in each of the first groups
+    disc = (bits.astype(np.uint64) & np.uint64((1 << discard_bits) - 1)) >> np.uint64(discard_bits - 16)   # top 16 discarded bits (normal result)
+    pick = rng.integers(0, 5, n)
+    h = rng.integers(0, 1 << 16, n, dtype=np.uint64)
+    h = np.where(pick == 0, disc, h)
+    h = np.where(pick == 1, (disc - 1) & 0xFFFF, h)
+    h = np.where(pick == 2, (disc + 1) & 0xFFFF, h)
+    h = np.where(rng.integers(0, 64, n) == 0, np.uint64(0), h)
+    h = np.where(rng.integers(0, 64, n) == 0, np.uint64(0xFFFF), h)
+    blocks = (h[0::2] | (h[1::2] << 16)).astype(np.uint32)                             # element 2j: low half of word j
+    return bits, np.ascontiguousarray(blocks)
+
+
+def test_stochastic_rounding_as_an_addition_equals_the_straight_line_cast(hc):
+    """sr_bf16_group8 / sr_fp8_group8 (one integer addition per element, the straight-line cast for groups near the top of
+    the range) against f32_to_bf16_flat<RM_SR> / f32_to_fp8_flat<RM_SR> with the same random halves."""
+    vp = lambda a: a.ctypes.data_as(C.c_void_p)
+    cases = [(abi.BF16, 0, 0, 0, 16)]   # (type, exponent width, bias, Inf/NaN convention, bits a normal result discards)
+    for ew, dt, biases, modes in ((4, abi.FP8_143, (3, 7, 11, 15), (0, 1, 2)), (5, abi.FP8_152, (15, 1, 24), (0, 2))):
+        cases += [(dt, ew, b, m, 23 - (7 - ew)) for b in biases for m in modes]
+    for dt, ew, bias, mode, discard in cases:
+        e_small = 128 - bias if ew else 1
+        e_top = (127 - bias + (1 << ew) - (1 if mode == 0 else 0)) if ew else 254
+        bits, blocks = sr_inputs(discard, e_small, e_top)
+        es = 2 if dt == abi.BF16 else 1
+        for clip, cii, canon in ((0, 0, 0), (1, 0, 1), (1, 1, 0)):
+            fast, flat = np.zeros(bits.size * es, np.uint8), np.zeros(bits.size * es, np.uint8)
+            hc.hc_sr_groups(vp(bits), vp(blocks), C.c_size_t(bits.size // 8), dt, ew, bias, mode, clip, cii, canon, vp(fast), vp(flat))
+            bad = np.nonzero(fast != flat)[0]
+            assert bad.size == 0, (dt, ew, bias, mode, clip, cii, hex(int(bits[bad[0] // es])), int(fast[bad[0]]), int(flat[bad[0]]))
+        # the two roundings must both occur (the change points are inside the sample)
+        assert len(np.unique(flat)) > (200 if es == 1 else 250)
+    c4, w8 = np.zeros(4, np.uint32), np.zeros(8, np.uint32)
+    hc.hc_philox_half.restype = C.c_uint32
+    hc.hc_philox_block8(C.c_uint64(9), C.c_uint64(16), C.c_uint64(4096), vp(c4), vp(w8))
+    assert [hc.hc_philox_half(C.c_uint64(9), C.c_uint64(16), C.c_uint64(4096 + i)) for i in range(8)] == w8.tolist()
+
+
 def test_philox_word_never_zero_and_uniform(hc):
     hc.hc_philox.restype = C.c_uint32
     w = np.array([hc.hc_philox(C.c_uint64(5), C.c_uint64(0), C.c_uint64(i)) for i in range(20000)], dtype=np.uint64)
