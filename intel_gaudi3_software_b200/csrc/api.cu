@@ -40,6 +40,7 @@ struct Tuning {
     int host_pipeline = -1;   // 0: host-tensor GEMMs are staged whole instead of pipelined
     int tile_n = -1;          // CTA-pair kernel: forced tile width (a multiple of 32 in [32, 256])
     int stream_k = -1;        // 0: never cut the tiles of a ragged last wave along K; 1: cut them whenever there is such a wave
+    int dependent_launch = -1;   // 0: the CTA-pair kernel is launched without programmatic stream serialisation
 };
 static int env_int(const char* name, int dflt) {
     const char* e = getenv(name);
@@ -313,7 +314,7 @@ static int launch_status(mmeb200_ctx* c, const LaunchResult& r) {
     c->launches++;
     return 0;
 }
-static LaunchEnv launch_env(const mmeb200_ctx* c) { return LaunchEnv{c->device, c->sm_count, c->stream}; }
+static LaunchEnv launch_env(const mmeb200_ctx* c) { return LaunchEnv{c->device, c->sm_count, c->stream, c->tune.dependent_launch != 0}; }
 
 struct GemmJob {
     TmaOperand a, b;
@@ -1134,6 +1135,7 @@ int mmeb200_create(mmeb200_ctx** out_ctx, int chip, int device, unsigned seed, u
     c->tune.host_pipeline = getenv("MME_B200_NO_HOST_PIPELINE") ? 0 : -1;
     c->tune.tile_n = env_int("MME_B200_TILE_N", -1);
     c->tune.stream_k = env_int("MME_B200_STREAM_K", -1);
+    c->tune.dependent_launch = env_int("MME_B200_DEPENDENT_LAUNCH", -1);
     if (cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) != cudaSuccess || cudaMalloc(&c->d_status, 64) != cudaSuccess ||
         cudaMallocHost(&c->h_status, 64) != cudaSuccess || cudaEventCreate(&c->ev0) != cudaSuccess || cudaEventCreate(&c->ev1) != cudaSuccess) {
         delete c;
@@ -1198,7 +1200,7 @@ int mmeb200_set_option(mmeb200_ctx* c, const char* name, int value) {
     struct { const char* name; int Tuning::*field; } const table[] = {
         {"pair", &Tuning::pair}, {"block_n", &Tuning::block_n}, {"split_k", &Tuning::split_k}, {"epi_groups", &Tuning::epi_groups},
         {"raster_gm", &Tuning::raster_gm}, {"tma_store", &Tuning::tma_store}, {"host_pipeline", &Tuning::host_pipeline},
-        {"tile_n", &Tuning::tile_n}, {"stream_k", &Tuning::stream_k}};
+        {"tile_n", &Tuning::tile_n}, {"stream_k", &Tuning::stream_k}, {"dependent_launch", &Tuning::dependent_launch}};
     for (const auto& t : table)
         if (strcmp(t.name, name) == 0) {
             c->tune.*(t.field) = value < 0 ? -1 : value;

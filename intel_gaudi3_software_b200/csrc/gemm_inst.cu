@@ -57,8 +57,19 @@ LaunchResult INST_NAME(const LaunchEnv& env, const GemmParams& p, uint64_t tiles
     constexpr int smem = PairSmem<INST_PAIR_EPI>::kTotal;
     constexpr int threads = PairSmem<INST_PAIR_EPI>::kThreads;
     const unsigned pairs = unsigned(tiles < uint64_t(cap) ? tiles : uint64_t(cap));
-    gemm_tcgen05_pair_kernel<INST_KIND, INST_PAIR_EPI><<<pairs * 2, threads, smem, env.stream>>>(p);
-    return {cudaGetLastError(), LAUNCH_OK, "pair kernel launch"};
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3(pairs * 2);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = env.stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = env.dependent_launch ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<INST_KIND, INST_PAIR_EPI>, p);
+    return {e != cudaSuccess ? e : cudaGetLastError(), LAUNCH_OK, "pair kernel launch"};
 }
 
 #else

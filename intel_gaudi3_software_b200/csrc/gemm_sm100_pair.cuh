@@ -104,7 +104,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<EPI_GROUPS>
     gemm_tcgen05_pair_kernel(const __grid_constant__ GemmParams p) {
     using S = PairSmem<EPI_GROUPS>;
     constexpr int STAGES = S::kStages;
+    if (p.pred) griddep_wait();   // the predicate word comes from an earlier kernel of the stream
     if (launch_is_predicated_off(p.pred, p.pred_nonzero)) return;   // uniform over the grid (both CTAs of every pair)
+    griddep_launch_dependents();   // all CTAs of this grid are resident: what frees up may go to the next kernel
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw;
     if (smem_u32(smem) & 1023u) {   // uniform over the cluster: both CTAs see the same offset
@@ -149,6 +151,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<EPI_GROUPS>
     cluster_sync_all();      // both CTAs' barriers are initialised and both allocations are done
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
+    // Set-up is done without touching global memory; everything below reads operands or writes results that a kernel
+    // earlier in the stream may produce or still use.
+    griddep_wait();
 
     if (warp == 0 || warp == 3) {
         // ------------------------------------------------------------------ TMA producers (warp 0: A, warp 3: B)

@@ -68,6 +68,13 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     }
 }
 
+// Programmatic dependent launch. A kernel launched with programmatic stream serialisation may become resident while
+// the kernel before it in the stream still runs; griddep_wait returns once that kernel has completed and its memory
+// operations are visible (at once in a launch without the attribute). griddep_launch_dependents lets the NEXT kernel in
+// the stream start becoming resident as SMs free up, instead of after this grid has drained.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // A word in global memory that another CTA of the same launch sets to `want` (st_release_gpu): wait for it, for at most
 // `limit_ns` nanoseconds. Returns false when the limit ran out.
 __device__ __forceinline__ void st_release_gpu(uint32_t* flag, uint32_t value) {
