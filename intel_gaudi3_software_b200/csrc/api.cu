@@ -39,7 +39,7 @@ struct Tuning {
     int tma_store = -1;       // 0: direct stores even where a TMA store applies
     int host_pipeline = -1;   // 0: host-tensor GEMMs are staged whole instead of pipelined
     int tile_n = -1;          // CTA-pair kernel: forced tile width (a multiple of 32 in [32, 256])
-    int stream_k = -1;        // 0: never cut the tiles of a ragged last wave along K; 1: cut them whenever there is such a wave
+    int stream_k = -1;        // 1: cut the tiles of a ragged last wave along K (CTA-pair kernel) whenever a cut exists
     int dependent_launch = -1;   // 0: the CTA-pair kernel is launched without programmatic stream serialisation
 };
 static int env_int(const char* name, int dflt) {
@@ -520,13 +520,15 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
         if (cap2) units = std::min(units, cap2);
     }
     // Cut tail: with whole tiles only, `tiles % units` tiles make a last wave that leaves pairs idle (1024 x 8192 outputs:
-    // 128 tiles on 74 pairs, 1.73 waves). Each of those tiles is cut along K into a head, computed by a pair of its own, and
-    // pieces that the remaining pairs share; the head's pair adds the pieces' sums and finishes the tile (PairSchedule,
-    // gemm_sm100_pair.cuh). Head and piece lengths are the ones that finish earliest; the cut pays when that beats a whole
-    // tile's k blocks by a margin: every piece costs 128 KB per CTA written and read again through L2, beside the operands.
+    // 128 tiles on 74 pairs, 1.73 waves). Each of those tiles can be cut along K into a head, computed by a pair of its own,
+    // and pieces that the remaining pairs share; the head's pair adds the pieces' sums and finishes the tile (PairSchedule,
+    // gemm_sm100_pair.cuh). Head and piece lengths are the ones that finish earliest by a cost model in k blocks. Measured,
+    // the cut does not pay on this part (a ragged wave runs its k blocks faster, the kernel being bound by the aggregate
+    // L2-to-SM operand rate; a piece's sums cost 128 KB per CTA written and read again beside that stream): it is taken
+    // only when the knob "stream_k" asks for it.
     uint64_t launch_pairs = tiles * split;
-    if (use_pair && split == 1 && !peer && tune.stream_k != 0 && units > 1) {
-        const uint64_t rem = tiles % units, waves = tiles / units + 1, helpers = units - rem;
+    if (use_pair && split == 1 && !peer && tune.stream_k > 0 && units > 1) {
+        const uint64_t rem = tiles % units, helpers = units - rem;
         const uint32_t nkb = p.num_k_blocks;
         uint32_t best_head = 0, best_piece = 0, best_pieces = 0;
         uint64_t best_cost = nkb;
@@ -538,15 +540,15 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
             // (about sixteen k blocks' time, measured)
             const uint64_t helper_time = ((rem * pieces + helpers - 1) / helpers) * std::max(piece, 16u);
             const uint64_t cost = std::max<uint64_t>(head, helper_time) + 4;
-            if (cost < best_cost || (tune.stream_k > 0 && best_head == 0)) {   // the knob takes any cut, the planner one that pays
+            if (cost < best_cost || best_head == 0) {   // the knob takes any cut; the cheapest one by the model
                 best_cost = std::min(cost, uint64_t(nkb)); best_head = head; best_piece = piece; best_pieces = pieces;
             }
             if (((rem * pieces + helpers - 1) / helpers) * piece <= head) break;   // longer heads only finish later
         }
-        const bool pays = best_head && (nkb - best_cost) * 100 >= 10 * waves * nkb;
-        if (best_head && (pays || tune.stream_k > 0)) {
-            // eight epilogue warps: adding a slot's sums is bound by the loads a warp keeps in flight
-            if (tune.epi_groups <= 0) two_groups = true;
+        if (best_head) {
+            // eight epilogue warps: adding a slot's sums is bound by the loads a warp keeps in flight (the cut-tail kernel
+            // exists in that form only)
+            two_groups = true;
             const uint32_t slots = uint32_t(rem) * best_pieces;
             if (c->sk_slots_cap < slots) {
                 if (c->sk_ws) { CUDA_OK(c, cudaStreamSynchronize(c->stream)); cudaFree(c->sk_ws); cudaFree(c->sk_flags); c->sk_ws = nullptr; c->sk_flags = nullptr; }

@@ -10,6 +10,8 @@ LaunchResult launch_gemm_single(const LaunchEnv& env, uint32_t kind, int block_n
 }
 
 LaunchResult launch_gemm_pair(const LaunchEnv& env, uint32_t kind, int epi_groups, const GemmParams& p, uint64_t tiles) {
+    if (p.sk_tiles != 0)
+        return kind == KIND_F16 ? launch_pair_f16_e2_cut(env, p, tiles) : kind == KIND_TF32 ? launch_pair_tf32_e2_cut(env, p, tiles) : launch_pair_f8_e2_cut(env, p, tiles);
     if (epi_groups == 2)
         return kind == KIND_F16 ? launch_pair_f16_e2(env, p, tiles) : kind == KIND_TF32 ? launch_pair_tf32_e2(env, p, tiles) : launch_pair_f8_e2(env, p, tiles);
     return kind == KIND_F16 ? launch_pair_f16_e1(env, p, tiles) : kind == KIND_TF32 ? launch_pair_tf32_e1(env, p, tiles) : launch_pair_f8_e1(env, p, tiles);

@@ -1,6 +1,6 @@
 // One instantiation of a tcgen05 GEMM kernel and its host launcher. The Makefile compiles this file once per
-// variant with  -DINST_NAME=<launcher name> -DINST_KIND=<KIND_*> and either -DINST_PAIR_EPI=<1|2> (CTA-pair
-// kernel) or -DINST_BLOCK_N=<128|256> -DINST_STAGES=<n> (single-CTA kernel).
+// variant with  -DINST_NAME=<launcher name> -DINST_KIND=<KIND_*> and either -DINST_PAIR_EPI=<1|2> -DINST_PAIR_CUT=<0|1>
+// (CTA-pair kernel) or -DINST_BLOCK_N=<128|256> -DINST_STAGES=<n> (single-CTA kernel).
 #include <cstring>
 
 #include "gemm_launch.h"
@@ -16,7 +16,7 @@ namespace mmeb200 {
 static int g_max_pairs[64] = {};
 
 static LaunchResult configure(const LaunchEnv& env, int* pairs) {
-    auto kern = gemm_tcgen05_pair_kernel<INST_KIND, INST_PAIR_EPI>;
+    auto kern = gemm_tcgen05_pair_kernel<INST_KIND, INST_PAIR_EPI, INST_PAIR_CUT != 0>;
     constexpr int smem = PairSmem<INST_PAIR_EPI>::kTotal;
     constexpr int threads = PairSmem<INST_PAIR_EPI>::kThreads;
     int& cached = g_max_pairs[env.device & 63];
@@ -68,7 +68,7 @@ LaunchResult INST_NAME(const LaunchEnv& env, const GemmParams& p, uint64_t tiles
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = env.dependent_launch ? 1 : 0;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<INST_KIND, INST_PAIR_EPI>, p);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<INST_KIND, INST_PAIR_EPI, INST_PAIR_CUT != 0>, p);
     return {e != cudaSuccess ? e : cudaGetLastError(), LAUNCH_OK, "pair kernel launch"};
 }
 

@@ -28,7 +28,8 @@ struct LaunchResult {
 
 // Single-CTA kernel, tile 128 x BLOCK_N (BLOCK_N = 256 with 4 stages, 128 with 6 stages).
 LaunchResult launch_gemm_single(const LaunchEnv& env, uint32_t kind, int block_n, const GemmParams& p, unsigned grid);
-// CTA-pair kernel, tile 256 x 256, with one or two groups of four epilogue warps. `tiles` counts (tile, split) work items;
+// CTA-pair kernel, tile 256 x 256, with one or two groups of four epilogue warps. A launch with a cut tail (p.sk_tiles != 0)
+// takes the instantiation built for it, which exists with two groups only. `tiles` counts (tile, split) work items;
 // the grid is the smaller of that and the number of CTA pairs the device holds at once.
 LaunchResult launch_gemm_pair(const LaunchEnv& env, uint32_t kind, int epi_groups, const GemmParams& p, uint64_t tiles);
 // Number of CTA pairs the device can hold at once for the given variant (0 on failure).
@@ -50,6 +51,9 @@ MMEB200_DECLARE_PAIR(launch_pair_f8_e1)
 MMEB200_DECLARE_PAIR(launch_pair_f16_e2)
 MMEB200_DECLARE_PAIR(launch_pair_tf32_e2)
 MMEB200_DECLARE_PAIR(launch_pair_f8_e2)
+MMEB200_DECLARE_PAIR(launch_pair_f16_e2_cut)
+MMEB200_DECLARE_PAIR(launch_pair_tf32_e2_cut)
+MMEB200_DECLARE_PAIR(launch_pair_f8_e2_cut)
 #undef MMEB200_DECLARE_SINGLE
 #undef MMEB200_DECLARE_PAIR
 

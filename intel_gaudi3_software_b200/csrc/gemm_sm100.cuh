@@ -600,6 +600,7 @@ __device__ __forceinline__ void store_row32(const uint32_t (&v)[32], uint8_t* ds
 // Epilogue of one output tile, run by one epilogue warp for its 32 rows: reads `tile_cols` accumulator columns (a
 // multiple of 32) from tensor memory (tmem_acc = the warp's lane window of the tile's accumulator), converts and stores
 // them. m0 is the first row of the CTA's 128-row block, n0 the first column.
+template <bool FIX = false>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tile_cols, uint32_t m0, uint32_t n0, uint32_t batch, uint32_t split,
                                               uint32_t tmem_acc, uint8_t* stage_out, uint32_t& store_buf, uint32_t sub, uint32_t lane,
                                               uint32_t out_elem, const SkFix& fix = SkFix{nullptr, 0u, 0u}) {
@@ -649,7 +650,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tile
             for (uint32_t l = 0; l < lds_per_chunk; ++l) {
                 uint32_t v[32];
                 tmem_ld_32x32b_x32(tmem_acc + ch * cols_per_chunk + l * 32, v);
-                tmem_ld_wait_add(v, fix, fix.col0 + ch * cols_per_chunk + l * 32, sub * 32 + lane);
+                if constexpr (FIX) tmem_ld_wait_add(v, fix, fix.col0 + ch * cols_per_chunk + l * 32, sub * 32 + lane);
+                else tmem_ld_wait();
                 epilogue_convert(v, p, out_elem, flat_row + col0 + l * 32);
                 if (out_elem == 4) {
 #pragma unroll
@@ -680,7 +682,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tile
     for (uint32_t c0 = done_cols; c0 < tile_cols; c0 += 32) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(tmem_acc + c0, v);
-        tmem_ld_wait_add(v, fix, fix.col0 + c0, sub * 32 + lane);
+        if constexpr (FIX) tmem_ld_wait_add(v, fix, fix.col0 + c0, sub * 32 + lane);
+        else tmem_ld_wait();
         const uint32_t col0 = n0 + c0;
         if (row >= p.M || col0 >= p.N) continue;
         const uint32_t ncols = min(32u, p.N - col0);

@@ -46,48 +46,57 @@ struct PairSmem {
 // tail or not, the whole tiles t = pair, pair + pairs, ... of the tiles before the cut ones.
 enum : uint32_t { WORK_TILE = 0, WORK_SK_WRITER = 1, WORK_SK_OWNER = 2 };
 constexpr uint32_t kNoSlot = 0xFFFFFFFFu;
-struct PairWork {
-    TileCoord tc;
-    uint32_t kind;
-    uint32_t slot;           // WORK_SK_WRITER: where this piece's running sum goes
-    uint32_t above;          // cut tiles: the slot with the running sum of the pieces after this one, or kNoSlot
-};
+// What next() hands out beside the tile's coordinates (cut-tail kernel only): kind (WORK_*), slot (WORK_SK_WRITER: where
+// this piece's running sum goes) and above (cut tiles: the slot with the running sum of the pieces after this one, or
+// kNoSlot). They are separate scalars, not a struct: every role keeps them in registers across its k loop.
+template <bool CUT>
 struct PairSchedule {
     uint32_t j;              // next piece of a helper pair (past the end for the others)
     uint32_t t;              // next whole tile
     bool head;               // the head of cut tile `pair` is still to do
+    uint32_t total;          // work items the planner counted: (tile, split) pairs, the cut tiles included
     __device__ __forceinline__ void init(const GemmParams& p, uint32_t pair) {
+        total = p.m_tiles * p.n_tiles * p.batches * p.split_k;
         t = pair;
-        head = p.sk_tiles != 0 && pair < p.sk_tiles;
-        j = (p.sk_tiles != 0 && pair >= p.sk_tiles) ? pair - p.sk_tiles : kNoSlot;
+        head = CUT && pair < p.sk_tiles;
+        j = (CUT && pair >= p.sk_tiles) ? pair - p.sk_tiles : kNoSlot;
     }
-    __device__ __forceinline__ bool next(const GemmParams& p, uint32_t pair, uint32_t num_pairs, PairWork& w) {
-        const uint32_t whole_tiles = p.m_tiles * p.n_tiles * p.batches * p.split_k - p.sk_tiles;
-        w.kind = WORK_TILE;
-        w.slot = 0;
-        w.above = kNoSlot;
+    __device__ __forceinline__ bool next(const GemmParams& p, uint32_t pair, uint32_t num_pairs, TileCoord& tc, uint32_t& kind, uint32_t& slot,
+                                         uint32_t& above) {
+        // the kernel without a cut tail: whole tiles only, and nothing else in the loop that every role runs between two tiles
+        // (recomputing the tile count there and three dead stores cost 3-7 % on the bf16 GEMM and the convolutions)
+        if constexpr (!CUT) {
+            if (t >= total) return false;
+            tc = decode_tile(p, t);
+            t += num_pairs;
+            return true;
+        }
+        kind = WORK_TILE;
+        slot = 0;
+        above = kNoSlot;
+        const uint32_t whole_tiles = total - p.sk_tiles;
         if (head) {
             head = false;
-            w.tc = decode_tile(p, whole_tiles + pair);
-            w.tc.kb_end = p.sk_head;
-            w.kind = WORK_SK_OWNER;
-            w.above = pair * p.sk_pieces;
+            tc = decode_tile(p, whole_tiles + pair);
+            tc.kb_end = p.sk_head;
+            kind = WORK_SK_OWNER;
+            above = pair * p.sk_pieces;
             return true;
         }
         if (j < p.sk_tiles * p.sk_pieces) {
             const uint32_t round = j / p.sk_tiles, tile = j - round * p.sk_tiles;
             const uint32_t piece = p.sk_pieces - round;
-            w.tc = decode_tile(p, whole_tiles + tile);
-            w.tc.kb_begin = p.sk_head + (piece - 1) * p.sk_piece;
-            w.tc.kb_end = min(p.num_k_blocks, w.tc.kb_begin + p.sk_piece);
-            w.kind = WORK_SK_WRITER;
-            w.slot = tile * p.sk_pieces + piece - 1;
-            if (piece < p.sk_pieces) w.above = w.slot + 1;
+            tc = decode_tile(p, whole_tiles + tile);
+            tc.kb_begin = p.sk_head + (piece - 1) * p.sk_piece;
+            tc.kb_end = min(p.num_k_blocks, tc.kb_begin + p.sk_piece);
+            kind = WORK_SK_WRITER;
+            slot = tile * p.sk_pieces + piece - 1;
+            if (piece < p.sk_pieces) above = slot + 1;
             j += num_pairs - p.sk_tiles;
             return true;
         }
         if (t < whole_tiles) {
-            w.tc = decode_tile(p, t);
+            tc = decode_tile(p, t);
             t += num_pairs;
             return true;
         }
@@ -99,7 +108,8 @@ struct PairSchedule {
 // multiple of 32) when that fills the last wave of tiles better: one MMA then covers 256 x tile_n, CTA `rank` stages the
 // columns from rank * tile_n / 2 on (whole 128-byte groups of an MN-major B: up to 16 bytes' worth of columns more than it
 // needs), and the epilogue leaves the columns after tile_n to the next tile.
-template <int KIND, int EPI_GROUPS>
+// CUT: the instantiation that can run a cut tail (p.sk_tiles != 0); the others carry none of its code.
+template <int KIND, int EPI_GROUPS, bool CUT = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<EPI_GROUPS>::kThreads, 1)
     gemm_tcgen05_pair_kernel(const __grid_constant__ GemmParams p) {
     using S = PairSmem<EPI_GROUPS>;
@@ -113,7 +123,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<EPI_GROUPS>
         if (threadIdx.x == 0) atomicCAS(p.status, 0u, SMEM_MISALIGNED);
         return;
     }
-    if (p.sk_tiles && (gridDim.x >> 1) <= p.sk_tiles) {   // nobody would compute the cut tiles' pieces
+    if (p.sk_tiles && (!CUT || (gridDim.x >> 1) <= p.sk_tiles)) {   // nobody would compute the cut tiles' pieces
         if (threadIdx.x == 0) atomicCAS(p.status, 0u, CUT_TAIL_WITHOUT_HELPERS);
         return;
     }
@@ -167,11 +177,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<EPI_GROUPS>
             const uint32_t my_bytes = is_a ? uint32_t(S::kABytes) : p.b_cta_bytes;
             const uint32_t dst_off = is_a ? 0u : uint32_t(S::kABytes);
             const uint32_t full0 = mapa_shared(smem_u32(&full_bar[0]), 0);   // the leader's full[0]
-            PairSchedule sched;
+            PairSchedule<CUT> sched;
             sched.init(p, pair);
-            PairWork work;
-            while (ok && sched.next(p, pair, num_pairs, work)) {
-                const TileCoord& tc = work.tc;
+            TileCoord tc;
+            uint32_t kind = WORK_TILE, slot = 0, above_slot = kNoSlot;
+            while (ok && sched.next(p, pair, num_pairs, tc, kind, slot, above_slot)) {
                 // first row (A) or column (B) this CTA stages
                 if (is_a) a_feed.begin_tile(p, tc.m0 * 2 + rank * kBlockM, tc.batch, tc.kb_begin);
                 else b_feed.begin_tile(p, tc.n0 * p.tile_n + rank * (p.tile_n / 2), tc.batch, tc.kb_begin);
@@ -206,11 +216,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<EPI_GROUPS>
             const uint64_t b_step = (p.b_mn_major ? mn_k_step : uint32_t(kUmmaKBytes)) >> 4;
             constexpr uint64_t kStageUnits = S::kStageBytes >> 4;
             const uint32_t idesc = p.idesc;   // M = 256, N = tile_n
-            PairSchedule sched;
+            PairSchedule<CUT> sched;
             sched.init(p, pair);
-            PairWork work;
-            while (ok && sched.next(p, pair, num_pairs, work)) {
-                const TileCoord& tc = work.tc;
+            TileCoord tc;
+            uint32_t kind = WORK_TILE, slot = 0, above_slot = kNoSlot;
+            while (ok && sched.next(p, pair, num_pairs, tc, kind, slot, above_slot)) {
                 if (!mbar_wait_bounded(&tmem_empty_bar[acc], acc_phase ^ 1, kWaitLimitNs)) {
                     atomicCAS(p.status, 0u, WAIT_MMA_TMEM_EMPTY);
                     break;
@@ -252,11 +262,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<EPI_GROUPS>
         uint8_t* stage_out = smem + STAGES * S::kStageBytes + grp * (2 * kBlockM * kRowBytes);
         uint32_t store_buf = 0;
         const uint32_t leader_tmem_empty = mapa_shared(smem_u32(&tmem_empty_bar[0]), 0);
-        PairSchedule sched;
+        PairSchedule<CUT> sched;
         sched.init(p, pair);
-        PairWork work;
-        while (sched.next(p, pair, num_pairs, work)) {
-            const TileCoord& tc = work.tc;
+        TileCoord tc;
+        uint32_t kind = WORK_TILE, slot = 0, above_slot = kNoSlot;
+        while (sched.next(p, pair, num_pairs, tc, kind, slot, above_slot)) {
             bool ready = mbar_wait_bounded(&tmem_full_bar[acc], acc_phase, kWaitLimitNs);
             ready = __all_sync(0xffffffffu, ready);
             if (!ready) {
@@ -266,26 +276,31 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairSmem<EPI_GROUPS>
             tc_fence_after_sync();
             const uint32_t tmem_acc = tmem_base + acc * kPairBlockN + grp * kGroupCols + ((sub * 32) << 16);
             const uint32_t group_cols = p.tile_n > grp * kGroupCols ? min(uint32_t(kGroupCols), p.tile_n - grp * kGroupCols) : 0u;
-            // a cut tile: wait for the running sum of the pieces after this one (none after the last piece)
-            const float* above = nullptr;
-            if (work.kind != WORK_TILE && work.above != kNoSlot) {
-                bool there = true;
-                if (lane == 0) there = flag_wait_bounded(p.sk_flags + (work.above * 2 + rank) * kSkFlagsPerCta + (warp - 4), p.sk_gen, kSkWaitLimitNs);
-                there = __all_sync(0xffffffffu, there);
-                if (there) above = p.sk_ws + uint64_t(work.above * 2 + rank) * kSkSlotFloats;
-                else atomicCAS(p.status, 0u, WAIT_STREAMK_PARTIAL);   // the tile is stored without the missing pieces; the call fails
-            }
-            if (work.kind == WORK_SK_WRITER) {
-                epilogue_partial(p.sk_ws + uint64_t(work.slot * 2 + rank) * kSkSlotFloats, above, grp * kGroupCols, group_cols, tmem_acc, sub * 32 + lane);
-                __syncwarp();
-                if (lane == 0) {
-                    __threadfence();
-                    st_release_gpu(p.sk_flags + (work.slot * 2 + rank) * kSkFlagsPerCta + (warp - 4), p.sk_gen);
+            if constexpr (CUT) {
+                // a cut tile: wait for the running sum of the pieces after this one (none after the last piece)
+                const float* above = nullptr;
+                if (kind != WORK_TILE && above_slot != kNoSlot) {
+                    bool there = true;
+                    if (lane == 0) there = flag_wait_bounded(p.sk_flags + (above_slot * 2 + rank) * kSkFlagsPerCta + (warp - 4), p.sk_gen, kSkWaitLimitNs);
+                    there = __all_sync(0xffffffffu, there);
+                    if (there) above = p.sk_ws + uint64_t(above_slot * 2 + rank) * kSkSlotFloats;
+                    else atomicCAS(p.status, 0u, WAIT_STREAMK_PARTIAL);   // the tile is stored without the missing pieces; the call fails
+                }
+                if (kind == WORK_SK_WRITER) {
+                    epilogue_partial(p.sk_ws + uint64_t(slot * 2 + rank) * kSkSlotFloats, above, grp * kGroupCols, group_cols, tmem_acc, sub * 32 + lane);
+                    __syncwarp();
+                    if (lane == 0) {
+                        __threadfence();
+                        st_release_gpu(p.sk_flags + (slot * 2 + rank) * kSkFlagsPerCta + (warp - 4), p.sk_gen);
+                    }
+                } else {
+                    const SkFix fix{above, above ? 1u : 0u, grp * kGroupCols};
+                    epilogue_tile<true>(p, group_cols, tc.m0 * 2 + rank * kBlockM, tc.n0 * p.tile_n + grp * kGroupCols, tc.batch, tc.split, tmem_acc,
+                                        stage_out, store_buf, sub, lane, out_elem, fix);
                 }
             } else {
-                const SkFix fix{above, above ? 1u : 0u, grp * kGroupCols};
                 epilogue_tile(p, group_cols, tc.m0 * 2 + rank * kBlockM, tc.n0 * p.tile_n + grp * kGroupCols, tc.batch, tc.split, tmem_acc,
-                              stage_out, store_buf, sub, lane, out_elem, fix);
+                              stage_out, store_buf, sub, lane, out_elem);
             }
             tc_fence_before_sync();
             __syncwarp();
