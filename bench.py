@@ -755,7 +755,7 @@ def run_ours(args):
         e2e["roofline"] = copy_bw
     line = {
         "metric": "GEMM/conv TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling if world > 1 else "weak",
+        "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling,   # the N = 1 line of a strong-scaling series says so too
         "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
         "config": config_dict(args.workload, world, scaling),
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roof, "sustained": sustained, "configs": configs,
@@ -871,7 +871,7 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": "GEMM/conv TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": t / args.steps * 1e3, "higher_is_better": True,
-        "scaling": scaling if world > 1 else "weak", "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
+        "scaling": args.scaling, "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
         "config": config_dict(args.workload, world, scaling),
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": lib.kind, "sample": sample_text(wl, rows),
                          "note": "the reference's CPU calculator on the host cores; each step is a bounded sample of the workload, "

@@ -335,12 +335,21 @@ __device__ __forceinline__ void epilogue_convert(uint32_t (&v)[32], const GemmPa
     if (p.epi_mode == EPI_BF16_RNE) {
         // round-to-nearest-even with no flags: the hardware conversion gives the reference's bits
         // (NaN -> 0x7FFF, denormals kept)
+        if (p.scale == 1.0f) {   // operands with the tensor cores' own exponent bias: nothing to fold
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const float lo = __uint_as_float(v[2 * j]) * p.scale, hi = __uint_as_float(v[2 * j + 1]) * p.scale;
-            uint32_t packed;
-            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
-            v[j] = packed;
+            for (int j = 0; j < 16; ++j) {
+                uint32_t packed;
+                asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(__uint_as_float(v[2 * j + 1])), "f"(__uint_as_float(v[2 * j])));
+                v[j] = packed;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float lo = __uint_as_float(v[2 * j]) * p.scale, hi = __uint_as_float(v[2 * j + 1]) * p.scale;
+                uint32_t packed;
+                asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
+                v[j] = packed;
+            }
         }
     } else if (p.epi_mode == EPI_F32) {
 #pragma unroll
