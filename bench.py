@@ -52,22 +52,20 @@ MULTI_GPU_CONFIGS = ["fp8_gemm_8192", "bf16_gemm_8192", "conv_fwd", "conv_dedx",
 # DRAM bytes per launch of the dominant kernel from an ncu capture (profiles/*.md say which command produced each
 # number); None where no capture exists.
 NCU_TRAFFIC_BYTES = {
-    "fp8_gemm_8192": 359.1e6,        # profiles/gemm_tcgen05_pair_fp8_gemm_8192.md
-    "fp8_gemm_8192_bias11": 359.1e6,  # same kernel and byte streams; only the epilogue scale differs
-    "fp8_gemm_8192_sr": 357.1e6,     # profiles/gemm_tcgen05_pair_epilogue_casts.md
-    "fp8_gemm_8192_fp8out": 277.1e6,
-    "fp8_gemm_8192_fp8out_sr": 276.8e6,
-    "bf16_gemm_8192": 1339.1e6,      # profiles/gemm_tcgen05_pair_other_workloads.md
-    "conv_fwd": 164.7e6,
-    "conv_dedx": 165.0e6,
-    "conv_dedw": 209.4e6,
-    "fp8_bgemm_attn": 2154.7e6,
-    "tf32_gemm_4096": 395.8e6,
-    "fp32_gemm_4096": 1107.4e6,
-    "cast_f32_to_bf16": 1581.7e6,    # profiles/simt_helper_kernels.md
-    "cast_f32_to_fp8": 1326.9e6,
-    "compare_bf16": 2152.2e6,
-    "memory_write_add_f32": 3180.7e6,
+    "fp8_gemm_8192": 352.9e6,        # profiles/gemm_tcgen05_pair_fp8_gemm_8192.md
+    "fp8_gemm_8192_bias11": 352.9e6,  # same kernel and byte streams; only the epilogue scale differs
+    "fp8_gemm_8192_sr": 352.6e6,     # profiles/gemm_tcgen05_pair_epilogue_casts.md
+    "fp8_gemm_8192_fp8out": 274.9e6,
+    "fp8_gemm_8192_fp8out_sr": 274.7e6,
+    "bf16_gemm_8192": 1353.4e6,      # profiles/gemm_tcgen05_pair_other_workloads.md
+    "conv_fwd": 165.6e6,
+    "conv_dedx": 165.1e6,
+    "conv_dedw": 209.0e6,
+    "fp8_bgemm_attn": 2154.3e6,
+    "tf32_gemm_4096": 393.7e6,
+    "fp32_gemm_4096": 1107.6e6,
+    "compare_bf16": 2153.2e6,        # profiles/simt_helper_kernels.md
+    "memory_write_add_f32": 3181.3e6,
 }
 
 

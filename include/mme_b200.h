@@ -179,7 +179,7 @@ int mmeb200_set_accumulation(mmeb200_ctx* ctx, int mode);
  * "epi_groups" (1/2), "raster_gm" (m tiles per raster group), "tma_store" (0 = direct stores), "host_pipeline"
  * (0 = host-tensor GEMMs staged whole), "tile_n" (CTA-pair kernel: tile width, a multiple of 32 up to 256), "stream_k"
  * (CTA-pair kernel: 1 = the tiles of a ragged last wave are cut along K among the CTA pairs wherever a cut exists; off by
- * default, it did not pay on the shapes measured), "dependent_launch" (0 = the CTA-pair kernel is launched without programmatic
+ * default, it did not pay on the shapes measured), "dependent_launch" (0 = the tcgen05 GEMM kernels are launched without programmatic
  * stream serialisation; with it, the kernel's set-up overlaps the tail of the kernel before it in the stream and it touches
  * memory only after that kernel has completed). The same knobs take their defaults from environment variables read once in
  * mmeb200_create (MME_B200_PAIR, MME_B200_BLOCK_N, MME_B200_SPLIT_K, MME_B200_EPI_GROUPS, MME_B200_GM,

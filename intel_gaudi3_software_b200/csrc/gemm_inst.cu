@@ -84,8 +84,19 @@ LaunchResult INST_NAME(const LaunchEnv& env, const GemmParams& p, unsigned grid)
         if (e != cudaSuccess) return {e, LAUNCH_OK, "cudaFuncSetAttribute(gemm kernel)"};
         g_configured[env.device & 63] = true;
     }
-    kern<<<grid, kGemmThreads, smem, env.stream>>>(p);
-    return {cudaGetLastError(), LAUNCH_OK, "gemm kernel launch"};
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = env.stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = env.dependent_launch ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+    return {e != cudaSuccess ? e : cudaGetLastError(), LAUNCH_OK, "gemm kernel launch"};
 }
 
 #endif

@@ -14,7 +14,7 @@ struct LaunchEnv {
     int device;
     int sm_count;
     cudaStream_t stream;
-    bool dependent_launch;   // CTA-pair kernel: launch with programmatic stream serialisation (set-up overlaps the previous kernel's tail)
+    bool dependent_launch;   // launch with programmatic stream serialisation (set-up overlaps the previous kernel's tail)
 };
 
 enum : int { LAUNCH_OK = 0, LAUNCH_NO_PAIR_FITS = -1 };

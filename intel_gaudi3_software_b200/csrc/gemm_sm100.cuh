@@ -712,7 +712,9 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tile
 template <int KIND, int BLOCK_N, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     using S = GemmSmem<BLOCK_N, STAGES>;
+    if (p.pred) griddep_wait();   // the predicate word comes from an earlier kernel of the stream
     if (launch_is_predicated_off(p.pred, p.pred_nonzero)) return;   // uniform over the grid, before anything is set up
+    griddep_launch_dependents();   // the next kernel of the stream may become resident as this grid's CTAs finish
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw;
     if (smem_u32(smem) & 1023u) {   // the operand stages and the staging buffers need 1024-byte alignment (128-byte swizzle)
@@ -751,6 +753,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
+    griddep_wait();   // set-up touched no global memory; what follows may depend on the kernel before this one
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer for A
