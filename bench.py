@@ -57,7 +57,7 @@ NCU_TRAFFIC_BYTES = {
     "fp8_gemm_8192_sr": 352.6e6,     # profiles/gemm_tcgen05_pair_epilogue_casts.md
     "fp8_gemm_8192_fp8out": 274.9e6,
     "fp8_gemm_8192_fp8out_sr": 274.7e6,
-    "bf16_gemm_8192": 1353.4e6,      # profiles/gemm_tcgen05_pair_other_workloads.md
+    "bf16_gemm_8192": 1173.7e6,      # profiles/gemm_tcgen05_pair_other_workloads.md
     "conv_fwd": 165.6e6,
     "conv_dedx": 165.1e6,
     "conv_dedw": 209.0e6,
