@@ -445,15 +445,7 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
         units = uint64_t(c->sm_count);
     }
     p.tile_n = tile_n;
-    // Raster group: the A panel of a group (its m tiles x all of K) should stay in L2 while the group's n tiles stream B
-    // past it. About 32 MiB does (the L2's two halves each keep their own copy of what both read): 16 m tiles of 256 rows
-    // for fp8 at K = 8192, 8 for bf16 (measured there: 8 is 3 % faster than 16, burst and sustained; for fp8 16 is 2 % faster
-    // than 8).
-    {
-        const uint64_t tile_bytes = uint64_t(use_pair ? 256 : kBlockM) * j.K * elem;
-        // 32-bit operands keep 16 (their K-major copies are three times as long for fp32; 4 measured 1 % slower there)
-        p.raster_gm = (elem <= 2 && 16 * tile_bytes > (uint64_t(32) << 20)) ? 8 : 16;
-    }
+    p.raster_gm = plan_raster_group(use_pair ? 256 : kBlockM, j.K, uint32_t(elem));   // schedule.cuh
     if (tune.raster_gm > 0) p.raster_gm = tune.raster_gm;
     tiles = uint64_t(p.m_tiles) * p.n_tiles * p.batches;
     uint32_t split = 1;
@@ -529,30 +521,17 @@ static int run_gemm(mmeb200_ctx* c, GemmJob& j, const OutSpec& o) {
     }
     // Cut tail: with whole tiles only, `tiles % units` tiles make a last wave that leaves pairs idle (1024 x 8192 outputs:
     // 128 tiles on 74 pairs, 1.73 waves). Each of those tiles can be cut along K into a head, computed by a pair of its own,
-    // and pieces that the remaining pairs share; the head's pair adds the pieces' sums and finishes the tile (PairSchedule,
-    // gemm_sm100_pair.cuh). Head and piece lengths are the ones that finish earliest by a cost model in k blocks. Measured,
+    // and pieces that the remaining pairs share; the head's pair adds the pieces' sums and finishes the tile (PairSchedule and
+    // plan_cut_tail, schedule.cuh). Head and piece lengths are the ones that finish earliest by a cost model in k blocks. Measured,
     // the cut does not pay on this part (a ragged wave runs its k blocks faster, the kernel being bound by the aggregate
     // L2-to-SM operand rate; a piece's sums cost 128 KB per CTA written and read again beside that stream): it is taken
     // only when the knob "stream_k" asks for it.
     uint64_t launch_pairs = tiles * split;
     if (use_pair && split == 1 && !peer && tune.stream_k > 0 && units > 1) {
-        const uint64_t rem = tiles % units, helpers = units - rem;
+        const uint64_t rem = tiles % units;
         const uint32_t nkb = p.num_k_blocks;
-        uint32_t best_head = 0, best_piece = 0, best_pieces = 0;
-        uint64_t best_cost = nkb;
-        for (uint32_t head = std::max(4u, uint32_t((rem * nkb + units - 1) / units)); rem != 0 && head < nkb; ++head) {
-            const uint32_t rest = nkb - head;
-            const uint32_t pieces = (rest + head - 1) / head, piece = (rest + pieces - 1) / pieces;
-            if (rem * pieces > 224 || piece < 2) break;
-            // a piece's pair is busy for the piece's k blocks or, if longer, for the epilogue that writes its sums
-            // (about sixteen k blocks' time, measured)
-            const uint64_t helper_time = ((rem * pieces + helpers - 1) / helpers) * std::max(piece, 16u);
-            const uint64_t cost = std::max<uint64_t>(head, helper_time) + 4;
-            if (cost < best_cost || best_head == 0) {   // the knob takes any cut; the cheapest one by the model
-                best_cost = std::min(cost, uint64_t(nkb)); best_head = head; best_piece = piece; best_pieces = pieces;
-            }
-            if (((rem * pieces + helpers - 1) / helpers) * piece <= head) break;   // longer heads only finish later
-        }
+        const CutPlan cut = plan_cut_tail(rem, units, nkb, true);
+        const uint32_t best_head = cut.head, best_piece = cut.piece, best_pieces = cut.pieces;
         if (best_head) {
             // eight epilogue warps: adding a slot's sums is bound by the loads a warp keeps in flight (the cut-tail kernel
             // exists in that form only)

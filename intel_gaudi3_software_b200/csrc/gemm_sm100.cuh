@@ -22,10 +22,10 @@
 #pragma once
 #include "numerics.cuh"
 #include "ptx_sm100.cuh"
+#include "schedule.cuh"
 
 namespace mmeb200 {
 
-constexpr int kBlockM = 128;
 constexpr int kRowBytes = 128;     // bytes of K per stage row = one swizzle span
 constexpr int kUmmaKBytes = 32;    // bytes of K consumed by one tcgen05.mma
 constexpr int kGemmThreads = 256;
@@ -185,30 +185,6 @@ struct GemmSmem {
     // wait-and-add kernels) to share the SM with it.
     static constexpr int kTotal = STAGES * kStageBytes + kOutStageBytes + kBarrierBytes;
 };
-
-struct TileCoord {
-    uint32_t m0, n0, batch, kb_begin, kb_end, split;
-};
-
-__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, uint32_t t) {
-    TileCoord c;
-    c.split = t % p.split_k;
-    t /= p.split_k;
-    const uint32_t per_batch = p.m_tiles * p.n_tiles;
-    c.batch = t / per_batch;
-    const uint32_t r = t % per_batch;
-    const uint32_t GM = p.raster_gm;
-    const uint32_t group_span = GM * p.n_tiles;
-    const uint32_t first_m = (r / group_span) * GM;
-    const uint32_t gsz = min(GM, p.m_tiles - first_m);
-    const uint32_t in_group = r % group_span;
-    c.m0 = (first_m + in_group % gsz) * kBlockM;
-    c.n0 = (in_group / gsz);  // tile index; scaled by the caller's BLOCK_N
-    const uint32_t per_split = (p.num_k_blocks + p.split_k - 1) / p.split_k;
-    c.kb_begin = c.split * per_split;
-    c.kb_end = min(p.num_k_blocks, c.kb_begin + per_split);
-    return c;
-}
 
 // One accumulator value before its cast: scale, NaN canonicalisation, optional ReLU.
 __device__ __forceinline__ uint32_t epilogue_prepare(uint32_t acc, const GemmParams& p) {

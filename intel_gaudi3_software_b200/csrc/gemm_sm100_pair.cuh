@@ -40,70 +40,6 @@ struct PairSmem {
     static constexpr int kThreads = 128 + 128 * EPI_GROUPS;
 };
 
-// The work items of one pair, in the order every role of both CTAs walks them. With a cut tail (p.sk_tiles != 0): pair
-// t < sk_tiles starts with the head of cut tile t; pair sk_tiles + h takes the pieces j = h, h + helpers, ... where piece j is
-// piece sk_pieces - j / sk_tiles (counted from 1, so a tile's later pieces come first) of cut tile j % sk_tiles. Then, cut
-// tail or not, the whole tiles t = pair, pair + pairs, ... of the tiles before the cut ones.
-enum : uint32_t { WORK_TILE = 0, WORK_SK_WRITER = 1, WORK_SK_OWNER = 2 };
-constexpr uint32_t kNoSlot = 0xFFFFFFFFu;
-// What next() hands out beside the tile's coordinates (cut-tail kernel only): kind (WORK_*), slot (WORK_SK_WRITER: where
-// this piece's running sum goes) and above (cut tiles: the slot with the running sum of the pieces after this one, or
-// kNoSlot). They are separate scalars, not a struct: every role keeps them in registers across its k loop.
-template <bool CUT>
-struct PairSchedule {
-    uint32_t j;              // next piece of a helper pair (past the end for the others)
-    uint32_t t;              // next whole tile
-    bool head;               // the head of cut tile `pair` is still to do
-    uint32_t total;          // work items the planner counted: (tile, split) pairs, the cut tiles included
-    __device__ __forceinline__ void init(const GemmParams& p, uint32_t pair) {
-        total = p.m_tiles * p.n_tiles * p.batches * p.split_k;
-        t = pair;
-        head = CUT && pair < p.sk_tiles;
-        j = (CUT && pair >= p.sk_tiles) ? pair - p.sk_tiles : kNoSlot;
-    }
-    __device__ __forceinline__ bool next(const GemmParams& p, uint32_t pair, uint32_t num_pairs, TileCoord& tc, uint32_t& kind, uint32_t& slot,
-                                         uint32_t& above) {
-        // the kernel without a cut tail: whole tiles only, and nothing else in the loop that every role runs between two tiles
-        // (recomputing the tile count there and three dead stores cost 3-7 % on the bf16 GEMM and the convolutions)
-        if constexpr (!CUT) {
-            if (t >= total) return false;
-            tc = decode_tile(p, t);
-            t += num_pairs;
-            return true;
-        }
-        kind = WORK_TILE;
-        slot = 0;
-        above = kNoSlot;
-        const uint32_t whole_tiles = total - p.sk_tiles;
-        if (head) {
-            head = false;
-            tc = decode_tile(p, whole_tiles + pair);
-            tc.kb_end = p.sk_head;
-            kind = WORK_SK_OWNER;
-            above = pair * p.sk_pieces;
-            return true;
-        }
-        if (j < p.sk_tiles * p.sk_pieces) {
-            const uint32_t round = j / p.sk_tiles, tile = j - round * p.sk_tiles;
-            const uint32_t piece = p.sk_pieces - round;
-            tc = decode_tile(p, whole_tiles + tile);
-            tc.kb_begin = p.sk_head + (piece - 1) * p.sk_piece;
-            tc.kb_end = min(p.num_k_blocks, tc.kb_begin + p.sk_piece);
-            kind = WORK_SK_WRITER;
-            slot = tile * p.sk_pieces + piece - 1;
-            if (piece < p.sk_pieces) above = slot + 1;
-            j += num_pairs - p.sk_tiles;
-            return true;
-        }
-        if (t < whole_tiles) {
-            tc = decode_tile(p, t);
-            t += num_pairs;
-            return true;
-        }
-        return false;
-    }
-};
-
 // p.m_tiles counts 256-row tiles here; p.n_tiles counts tiles of p.tile_n columns. The planner narrows tile_n (a
 // multiple of 32) when that fills the last wave of tiles better: one MMA then covers 256 x tile_n, CTA `rank` stages the
 // columns from rank * tile_n / 2 on (whole 128-byte groups of an MN-major B: up to 16 bytes' worth of columns more than it

@@ -6,6 +6,7 @@
 
 #include "numerics.cuh"
 #include "gaudi3_exact.cuh"
+#include "schedule.cuh"
 
 using namespace mmeb200;
 
@@ -163,6 +164,44 @@ void hc_philox_block8(uint64_t seed, uint64_t offset, uint64_t index8, uint32_t*
     philox_block8(seed, offset, index8, c);
     for (int i = 0; i < 4; i++) c4[i] = c[i];
     for (int e = 0; e < 8; e++) words8[e] = philox_block8_word(c, e);
+}
+// The schedule the CTA-pair kernel walks (schedule.cuh), on the host: the planner's cut for `tiles` tiles of nkb k blocks on
+// `units` pairs, and the work items of one pair. An item is 8 words: m0, n0, batch, kb_begin, kb_end, kind, slot, above.
+struct HostSchedParams {
+    uint32_t m_tiles, n_tiles, batches, split_k, raster_gm, num_k_blocks, sk_tiles, sk_head, sk_piece, sk_pieces;
+};
+uint64_t hc_plan_cut_tail(uint64_t rem, uint64_t units, uint32_t nkb, int any, uint32_t* head_piece_pieces)
+{
+    const CutPlan c = plan_cut_tail(rem, units, nkb, any != 0);
+    head_piece_pieces[0] = c.head; head_piece_pieces[1] = c.piece; head_piece_pieces[2] = c.pieces;
+    return c.cost;
+}
+uint32_t hc_plan_raster_group(uint64_t tile_rows, uint64_t K, uint32_t elem) { return plan_raster_group(tile_rows, K, elem); }
+int hc_schedule_items(const uint32_t* params10, int cut, uint32_t pair, uint32_t num_pairs, uint32_t* items, int max_items)
+{
+    HostSchedParams p;
+    memcpy(&p, params10, sizeof p);
+    TileCoord tc{};
+    uint32_t kind = WORK_TILE, slot = 0, above = kNoSlot;
+    int n = 0;
+    auto put = [&]() {
+        if (n < max_items) {
+            uint32_t* o = items + 8 * n;
+            o[0] = tc.m0; o[1] = tc.n0; o[2] = tc.batch; o[3] = tc.kb_begin; o[4] = tc.kb_end; o[5] = kind; o[6] = slot; o[7] = above;
+        }
+        ++n;
+    };
+    if (cut) {
+        PairSchedule<true> s;
+        s.init(p, pair);
+        while (s.next(p, pair, num_pairs, tc, kind, slot, above)) put();
+    } else {
+        PairSchedule<false> s;
+        s.init(p, pair);
+        kind = WORK_TILE; slot = 0; above = kNoSlot;
+        while (s.next(p, pair, num_pairs, tc, kind, slot, above)) put();
+    }
+    return n;
 }
 void hc_philox_block(uint32_t* c, uint32_t k0, uint32_t k1)
 {

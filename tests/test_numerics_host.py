@@ -19,7 +19,8 @@ SO = os.path.join(ROOT, "tests", "hostcheck", "libnumerics_host.so")
 @pytest.fixture(scope="module")
 def hc():
     inc = os.path.join(ROOT, "intel_gaudi3_software_b200", "csrc")
-    if not os.path.exists(SO) or os.path.getmtime(SO) < max(os.path.getmtime(SRC), os.path.getmtime(os.path.join(inc, "numerics.cuh"))):
+    newest = max(os.path.getmtime(f) for f in [SRC] + [os.path.join(inc, h) for h in ("numerics.cuh", "schedule.cuh", "gaudi3_exact.cuh")])
+    if not os.path.exists(SO) or os.path.getmtime(SO) < newest:
         subprocess.check_call(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-I" + inc, "-o", SO, SRC])
     return C.CDLL(SO)
 
